@@ -1,0 +1,331 @@
+"""MoE-layer tokens/s on synthetic Qwen3-30B-A3B-shaped layers (decode headline, prefill beside it).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one forward of one packed MoE layer over one batch of tokens: route -> basis
+projections -> packed experts -> down basis.  The timed loop rotates over `--layers` distinct
+weight sets (more than two L2s of packed bytes) so every step streams its experts from HBM.
+Rank 0 prints one JSON line.  `--impl reference` times the CPU dequantise-then-matmul path on
+the host cores instead (the reference ships no CPU forward; see oracle/cpu_path.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "moe_layer_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tokens", type=int, default=64, help="decode batch of the headline number")
+    ap.add_argument("--layers", type=int, default=12, help="distinct weight sets rotated through")
+    ap.add_argument("--prefill-tokens", type=int, default=8192)
+    ap.add_argument("--no-extras", action="store_true", help="headline only (skip other batch sizes / prefill / cpu)")
+    ap.add_argument("--path", type=int, default=0, help="experts path: 0 auto, 1 generic, 2 decode, 3 tensor")
+    return ap.parse_args()
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------- CPU arm
+def cpu_layer_from(layer, top_k, weight_dtype):
+    import numpy as np
+    from oracle import cpu_path
+
+    def host(t):
+        t = t.detach().cpu()
+        return t.to(torch.int64).numpy().astype(np.uint32) if t.dtype == torch.uint32 else t.numpy()
+
+    E = layer.cfg.num_experts
+    experts = [{tag: {f + "_buffer": host(layer.tables[tag][f][e]) for f in layer.tables[tag]} for tag in ("gate", "up", "down")}
+               for e in range(E)]
+    return cpu_path.CpuLayer(experts, layer.vh_gate.cpu(), layer.vh_up.cpu(), layer.u_down.cpu(), layer.cfg.intermediate,
+                             top_k, layer.cfg.norm_topk_prob, weight_dtype)
+
+
+def time_cpu(layer, tokens, steps, warmup):
+    from bitsmoe_b200 import synth
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cl = cpu_layer_from(layer, layer.cfg.top_k, torch.bfloat16)
+    x = synth.activations(layer.cfg, tokens, seed=1)
+    logits = synth.router_logits(layer.cfg, tokens, seed=2)
+    for _ in range(warmup):
+        cl.forward(x, logits)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cl.forward(x, logits)
+    dt = (time.perf_counter() - t0) / steps
+    return tokens / dt, dt, cores
+
+
+def reference_arm(args):
+    rank, world, _ = dist_env(args)
+    if rank != 0:
+        return
+    from bitsmoe_b200 import synth
+    cfg = synth.QWEN3_30B
+    layer = synth.make_layer(cfg, seed=42, device="cpu")
+    steps = max(1, min(args.steps, 20))
+    warm = max(1, min(args.warmup, 2))
+    tps, dt, cores = time_cpu(layer, args.tokens, steps, warm)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"qwen3-30b-a3b moe layer decode, {args.tokens} tokens, mixed 2/3/4-bit (0.8/0.15/0.05)",
+                   "tokens": args.tokens, "experts": cfg.num_experts, "top_k": cfg.top_k},
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{steps} forwards of one layer, {args.tokens} tokens, dequantise-then-matmul fp32"},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------- GPU arm
+def timed(fn, steps, stream_sync):
+    """CUDA-event time of `steps` calls of fn(i) on the current stream, in ms."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream_sync()
+    start.record()
+    for i in range(steps):
+        fn(i)
+    stop.record()
+    stream_sync()
+    return start.elapsed_time(stop)
+
+
+def active_expert_bytes(packed, offsets_cpu):
+    n = 0
+    act = 0
+    for e in range(packed.num_experts):
+        if offsets_cpu[e + 1] > offsets_cpu[e]:
+            n += packed.expert_bytes(e)
+            act += 1
+    return n, act
+
+
+def gpu_arm(args):
+    from bitsmoe_b200 import capi, synth
+    from bitsmoe_b200.layer import route_build, route_topk
+    rank, world, local = dist_env(args)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = synth.QWEN3_30B
+    pk = peaks()
+    L = args.layers
+    layers = [synth.to_packed_layer(synth.make_layer(cfg, seed=42 + i + 1000 * rank, device=dev), dev) for i in range(L)]
+    sync = lambda: torch.cuda.synchronize(dev)
+
+    def barrier():
+        sync()
+        if world > 1:
+            torch.distributed.barrier()
+            sync()
+
+    def decode_case(T, steps, warmup, want_roofline):
+        xs = [synth.activations(cfg, T, seed=7 + i, device=dev) for i in range(L)]
+        lg = [synth.router_logits(cfg, T, seed=9 + i, device=dev) for i in range(L)]
+        ys = [torch.empty_like(xs[0]) for _ in range(L)]
+        step = lambda i: layers[i % L].forward(xs[i % L], lg[i % L], cfg.top_k, True, torch.bfloat16, out=ys[i % L], path=args.path)
+        for i in range(max(warmup, 3)):
+            step(i)
+        barrier()
+        ms = timed(step, steps, sync)
+        out = {"tokens": T, "ms_per_step": ms / steps, "tokens_per_s": T * steps / (ms * 1e-3)}
+        if want_roofline:
+            # dominant kernel alone: the packed-experts stage on prepared routing, same rotation
+            prep = []
+            for i in range(L):
+                idx, w = route_topk(lg[i], cfg.top_k, True, torch.bfloat16)
+                tok, off, rw, _, _ = route_build(idx, w, cfg.num_experts)
+                hg, hu = layers[i].basis_project(xs[i])
+                prep.append((hg, hu, tok, off, rw))
+            est = lambda i: layers[i % L].experts_forward(*prep[i % L], path=args.path)
+            for i in range(3):
+                est(i)
+            ems = timed(est, steps, sync) / steps
+            byts = 0
+            act = 0
+            for i in range(L):
+                b, a = active_expert_bytes(layers[i], prep[i][3].cpu().tolist())
+                byts += b
+                act += a
+            byts = byts / L + T * cfg.rank * 2 * 2 + T * cfg.top_k * 8 + (cfg.num_experts + 1) * 4 + T * cfg.rank * 4
+            out["experts_kernel_ms"] = ems
+            out["experts_bytes"] = byts
+            out["active_experts"] = act / L
+        return out
+
+    def e2e_case(T, steps, warmup):
+        hx = [synth.activations(cfg, T, seed=70 + i).pin_memory() for i in range(4)]
+        hl = [synth.router_logits(cfg, T, seed=90 + i).pin_memory() for i in range(4)]
+        hy = torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory()
+        dx = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=dev)
+        dl = torch.empty((T, cfg.num_experts), dtype=torch.float32, device=dev)
+        dy = torch.empty_like(dx)
+
+        def step(i):
+            dx.copy_(hx[i % 4], non_blocking=True)
+            dl.copy_(hl[i % 4], non_blocking=True)
+            layers[i % L].forward(dx, dl, cfg.top_k, True, torch.bfloat16, out=dy, path=args.path)
+            hy.copy_(dy, non_blocking=True)
+        for i in range(max(warmup, 3)):
+            step(i)
+        barrier()
+        ms = timed(step, steps, sync)
+        return {"value": T * steps / (ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": dx.numel() * 2 + dl.numel() * 4,
+                "d2h_bytes_per_step": dy.numel() * 2}
+
+    with ClockSampler(local) as clk:
+        head = decode_case(args.tokens, args.steps, args.warmup, True)
+        e2e = e2e_case(args.tokens, args.steps, args.warmup)
+    clocks = clk.summary()
+
+    extra = {}
+    if not args.no_extras:
+        for T in (1, 8, 32):
+            extra[f"decode_{T}"] = decode_case(T, args.steps, args.warmup, True)
+        try:
+            Tp = args.prefill_tokens
+            xs = synth.activations(cfg, Tp, seed=3, device=dev)
+            lg = synth.router_logits(cfg, Tp, seed=4, zipf_s=1.1, device=dev)
+            yo = torch.empty_like(xs)
+            pstep = lambda i: layers[i % L].forward(xs, lg, cfg.top_k, True, torch.bfloat16, out=yo, path=args.path)
+            for i in range(2):
+                pstep(i)
+            n = max(2, min(args.steps, 5))
+            pms = timed(pstep, n, sync) / n
+            flops = Tp * cfg.top_k * 3 * 2 * cfg.rank * cfg.intermediate + Tp * 3 * 2 * cfg.hidden * cfg.rank
+            extra[f"prefill_{Tp}"] = {"tokens": Tp, "ms_per_step": pms, "tokens_per_s": Tp / (pms * 1e-3),
+                                      "tflops": flops / (pms * 1e-3) / 1e12,
+                                      "frac_of_bf16_peak": flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], "router": "zipf 1.1"}
+        except Exception as ex:  # keep the headline if the large case fails
+            extra["prefill_error"] = repr(ex)
+
+    value = head["tokens_per_s"]
+    ms_step = head["ms_per_step"]
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms_step, e2e["value"]], device=dev, dtype=torch.float64)
+        mx = t.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        mn = t.clone()
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        ms_step = float(mx[0])
+        value = world * args.tokens / (ms_step * 1e-3)
+        e2e["value"] = float(mn[1]) * world
+    if rank != 0:
+        return
+    achieved = head["experts_bytes"] / (head["experts_kernel_ms"] * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": f"qwen3-30b-a3b moe layer decode, {args.tokens} tokens per GPU, mixed 2/3/4-bit "
+                               "(0.8/0.15/0.05), rank-256 shared basis, top-8 of 128 experts",
+                   "tokens_per_gpu": args.tokens, "layers_rotated": L,
+                   "l2": f"inputs larger than L2: {L} distinct weight sets of ~23 MB rotate through the timed loop",
+                   "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas"},
+        "e2e": e2e, "gpu_launches": 5 * args.steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                     "kernel": "packed experts stage", "kernel_ms": head["experts_kernel_ms"],
+                     "algorithmic_bytes": head["experts_bytes"], "active_experts": head["active_experts"]},
+        "extra": extra,
+    }
+    if not args.no_extras:
+        cpu_layer = synth.make_layer(cfg, seed=42, device=dev)
+        cpu_layer.tables = {t: {f: [x.cpu() for x in v] for f, v in fl.items()} for t, fl in cpu_layer.tables.items()}
+        tps, dt, cores = time_cpu(cpu_layer, args.tokens, 3, 1)
+        line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"3 forwards of one layer, {args.tokens} tokens, dequantise-then-matmul fp32 "
+                                          f"({dt * 1e3:.0f} ms each)"}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        reference_arm(a)
+    else:
+        gpu_arm(a)

@@ -1,0 +1,123 @@
+// Shared declarations of the bitsmoe_b200 library (host + device).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <vector>
+
+#include "../../include/bitsmoe_b200.h"
+
+namespace bm {
+
+constexpr int K_SLAB = 64;     // rows per slab at most
+constexpr int N_TILE = 128;    // columns per scale group
+constexpr int K_STAGE = 16;    // rows per payload stage
+constexpr int N_MICRO = 32;    // columns per bit-plane word
+constexpr int MICROS = N_TILE / N_MICRO;
+
+int set_error(int status, const char* fmt, ...);
+
+#define BM_REQUIRE(cond, status, ...)                       \
+  do {                                                      \
+    if (!(cond)) return ::bm::set_error((status), __VA_ARGS__); \
+  } while (0)
+
+#define BM_CUDA(expr)                                                                   \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess)                                                              \
+      return ::bm::set_error(BM_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
+  } while (0)
+
+#define BM_LAUNCH_CHECK(name)                                                              \
+  do {                                                                                     \
+    cudaError_t _e = cudaGetLastError();                                                   \
+    if (_e != cudaSuccess)                                                                 \
+      return ::bm::set_error(BM_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
+  } while (0)
+
+// One packed matrix as the device sees it (pointers into the caller's buffers).
+struct MatDev {
+  const uint32_t* payload;
+  const int32_t* rank_idx;
+  const int32_t* tile_meta;
+  const int32_t* slab_meta;
+  const __half* scale;
+  const __half* s;
+  int32_t n_slabs;
+  int32_t n_tile_rows;
+  int32_t n_rows;
+  int32_t pad_;
+};
+
+struct ExpertDev {
+  MatDev m[3];
+};
+
+// Host mirror of one slab (validated at plan time).
+struct SlabHost {
+  int32_t bits, k_slab, rank_off, tile_off, tile_end;
+};
+
+struct MatHost {
+  std::vector<SlabHost> slabs;
+  std::vector<int32_t> tile_meta;  // [n_tile_rows * 3]
+  int64_t bytes = 0;               // as stored by the reference
+  int32_t n_rows = 0;
+};
+
+__host__ __device__ inline int words_per_row(int bits) { return bits == 16 ? 16 : bits; }
+
+__host__ __device__ inline int code_offset(int bits) {
+  // u = q + offset for bits > 1; the 1-bit case is q = 2u - 1.
+  return bits == 1 ? 0 : (1 << (bits - 1));
+}
+
+inline bool supported_bits(int b) { return b == 1 || b == 2 || b == 3 || b == 4 || b == 6 || b == 8 || b == 16; }
+
+__device__ __forceinline__ float load_act(const void* p, int dtype, int64_t i) {
+  if (dtype == BM_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  if (dtype == BM_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+  return reinterpret_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ void store_act(void* p, int dtype, int64_t i, float v) {
+  if (dtype == BM_F16) reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+  else if (dtype == BM_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(p)[i] = v;
+}
+
+// C[M,N] = A[M,K] . B[N,K]^T ; up to two problems sharing A's shape in one launch.
+struct GemmArgs {
+  const void* A[2];
+  const __half* B[2];
+  void* C[2];
+  const void* residual;  // same dtype / shape as C, problem 0 only
+  int a_dtype, c_dtype;
+  int round_a_f16;       // round an fp32 A through fp16 first (rank_accum.half())
+  int M, N, K;
+};
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace bm
+
+struct bm_layer {
+  int32_t num_experts = 0, hidden = 0, intermediate = 0, rank_in = 0, rank_out = 0, n_tiles = 0;
+  int32_t max_rows = 0;            // largest n_rows over all matrices
+  int device = 0;
+  const __half* vh_gate = nullptr;
+  const __half* vh_up = nullptr;
+  const __half* u_down = nullptr;
+  std::vector<bm::MatHost> host[3];   // [which][expert]
+  std::vector<bm_matrix_t> src[3];    // caller's descriptors (pointers kept)
+  bm::ExpertDev* experts_dev = nullptr;  // in the arena
+  void* arena = nullptr;
+  size_t arena_bytes = 0;
+  bool fast_ok = false;            // every slab is 2/3/4-bit and shapes fit the tensor / decode paths
+};

@@ -1,0 +1,157 @@
+/*
+ * bitsmoe_b200 -- C ABI of the sm_100a quantized-expert forward path.
+ *
+ * Every entry point returns an int status (BM_OK == 0), takes plain device
+ * pointers, element counts and the CUDA stream to enqueue on (passed as
+ * void*, i.e. a cudaStream_t), never allocates or frees device memory (the
+ * caller owns the arena, the workspace and all tensors), never synchronises
+ * the stream unless stated, and never traps: a failed check returns a status
+ * and bm_last_error() gives the message for the calling thread.
+ *
+ * Each declaration names the reference interface it stands in for, by the
+ * file's path inside the BitsMoE tree.
+ */
+#ifndef BITSMOE_B200_H_
+#define BITSMOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define BM_API __attribute__((visibility("default")))
+#else
+#define BM_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  BM_OK = 0,
+  BM_ERR_INVALID_ARG = 1,   /* shape / dtype / null pointer / inconsistent meta (TORCH_CHECK in the reference) */
+  BM_ERR_UNSUPPORTED = 2,   /* bit width, activation or size outside what the kernels implement */
+  BM_ERR_CUDA = 3,          /* a CUDA runtime call or a launch failed */
+  BM_ERR_WORKSPACE = 4,     /* caller-provided arena / workspace too small or misaligned */
+  BM_ERR_TIMEOUT = 5        /* a bounded device-side wait gave up; outputs are undefined */
+};
+
+enum { BM_F16 = 0, BM_BF16 = 1, BM_F32 = 2 };          /* element types of activations */
+enum { BM_ROUND_NONE = 0, BM_ROUND_F16 = 1, BM_ROUND_BF16 = 2 };
+enum { BM_PATH_AUTO = 0, BM_PATH_GENERIC = 1, BM_PATH_DECODE = 2, BM_PATH_TENSOR = 3 };
+enum { BM_GATE = 0, BM_UP = 1, BM_DOWN = 2 };
+
+BM_API int bm_abi_version(void);
+BM_API const char* bm_last_error(void);
+BM_API const char* bm_status_string(int status);
+
+/* ---- bit-plane codec ---------------------------------------------------
+ * Replaces pack_int8_{1,2,3,4,6,8}bit / unpack_int8_{...}bit of
+ * bitsmoe/quant/bitpack/bitpack_cuda_binding.cpp:37-65 (kernels
+ * bitsmoe/quant/bitpack/bitpack_cuda_kernel.cu:81-121, :157-196).
+ * q: int8 [rows, cols]; words: uint32 [rows, ceil(cols/32) * bits].
+ * Unpack writes int8 [rows, groups * 32]. */
+BM_API int bm_pack_bitplanes_i8(const int8_t* q, uint32_t* words, int64_t rows, int64_t cols, int bits, void* stream);
+BM_API int bm_unpack_bitplanes_i8(const uint32_t* words, int8_t* q, int64_t rows, int64_t groups, int bits, void* stream);
+
+/* ---- layer state -------------------------------------------------------
+ * One packed expert matrix exactly as the reference stores it: the six
+ * buffers that bitsmoe/models/base_mlp.py:96-102 registers and
+ * bitsmoe/algorithms/cpp/mlp_forward_binding.cpp:58-75 receives. */
+typedef struct {
+  const uint32_t* payload;     int64_t payload_words;
+  const int32_t*  rank_idx;    int32_t n_rows;        /* local row -> logical rank */
+  const int32_t*  tile_meta;   int32_t n_tile_rows;   /* [n_tile_rows, 3] = pack_off, scale_off, n_valid */
+  const int32_t*  slab_meta;   int32_t n_slabs;       /* [n_slabs, 4] = bits, k_slab, rank_off, tile_off */
+  const uint16_t* scale;       int64_t n_scales;      /* fp16 bits */
+  const uint16_t* s;                                  /* fp16 bits, n_rows entries */
+} bm_matrix_t;
+
+typedef struct {
+  int32_t num_experts;         /* packed (local) experts E' */
+  int32_t hidden;              /* H */
+  int32_t intermediate;        /* I */
+  int32_t rank_in;             /* rows of shared_vh_{gate,up}_proj == width of h_gate / h_up */
+  int32_t rank_out;            /* columns of shared_u_down == width of rank_accum */
+  int32_t act_type;            /* 0 = SiLU; anything else is BM_ERR_UNSUPPORTED (mlp_forward_binding.cpp:126) */
+  const bm_matrix_t* gate;     /* host array [num_experts] */
+  const bm_matrix_t* up;
+  const bm_matrix_t* down;
+  const uint16_t* vh_gate;     /* fp16 [rank_in, hidden]  (base_block.py:27), may be NULL for op-only use */
+  const uint16_t* vh_up;       /* fp16 [rank_in, hidden]  (base_block.py:28) */
+  const uint16_t* u_down;      /* fp16 [hidden, rank_out] (base_block.py:29) */
+} bm_layer_desc_t;
+
+typedef struct bm_layer bm_layer_t;
+
+/* Bytes of device arena a layer needs (pointer tables + repacked payload).  Reads the
+ * small meta buffers back to the host (synchronous), validates every offset against
+ * the buffer lengths, and takes the place of build_packed_meta_cached
+ * (bitsmoe/algorithms/cpp/mlp_forward.cu:2529-2697). */
+BM_API int bm_layer_plan(const bm_layer_desc_t* desc, size_t* arena_bytes);
+/* Builds the layer into caller-owned device memory `arena` (256-byte aligned,
+ * >= arena_bytes).  The reference buffers named by desc must stay alive: the generic
+ * path reads them in place.  Synchronises `stream` before returning. */
+BM_API int bm_layer_create(const bm_layer_desc_t* desc, void* arena, size_t arena_bytes, void* stream, bm_layer_t** out);
+BM_API int bm_layer_destroy(bm_layer_t* layer);
+/* Bytes the forward path reads for the experts, as stored by the reference
+ * (payload + scale + s + rank_idx + meta of the three matrices of expert e). */
+BM_API int64_t bm_layer_expert_bytes(const bm_layer_t* layer, int32_t expert);
+/* Decoded integer codes of one matrix through the arena (repacked) layout:
+ * int8 [n_rows, intermediate], local-row order.  For the bit-exactness tests. */
+BM_API int bm_layer_decode_codes(const bm_layer_t* layer, int32_t expert, int32_t which, int8_t* codes, void* stream);
+
+/* ---- routing -----------------------------------------------------------
+ * Router tail of bitsmoe/models/qwen3moe/bitsmoe_block.py:47-51 (softmax in
+ * fp32, top-k sorted by descending probability with ties to the lower expert
+ * id, optional renormalisation, weights rounded through `weight_round`).
+ * logits [T, E] of logits_dtype -> topk_idx int32 [T, k], topk_w fp32 [T, k]. */
+BM_API int bm_route_topk(const void* logits, int logits_dtype, int32_t T, int32_t E, int32_t k, int32_t renorm,
+                  int32_t weight_round, int32_t* topk_idx, float* topk_w, void* stream);
+BM_API size_t bm_route_build_workspace_bytes(int32_t T, int32_t k, int32_t num_local);
+/* _build_packed_routing of bitsmoe/models/base_block.py:258-289 plus the task
+ * tables of bitsmoe/algorithms/cpp/mlp_forward.cu:331-374, without host syncs:
+ *   token_indices int32 [T*k]   expert-contiguous, ascending (token, slot) inside an expert
+ *   expert_offsets int32 [num_local+1]
+ *   route_flat fp32 [T*k]
+ *   tile_table int32 [max_tiles, 3] = (expert, first assignment, rows <= tile_rows), padded
+ *              with rows == 0 entries up to max_tiles = bm_route_max_tiles(); may be NULL
+ *   counts int32 [2] = {assignments kept, tiles}; may be NULL
+ * global_to_local int32 [E] maps a routed expert id to a packed id or -1 (NULL = identity). */
+BM_API int32_t bm_route_max_tiles(int32_t T, int32_t k, int32_t num_local, int32_t tile_rows);
+BM_API int bm_route_build(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local,
+                   int32_t T, int32_t k, int32_t num_local, int32_t tile_rows,
+                   int32_t* token_indices, int32_t* expert_offsets, float* route_flat,
+                   int32_t* tile_table, int32_t* counts, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- forward stages ----------------------------------------------------
+ * h_gate = x @ Vh_gate^T, h_up = x @ Vh_up^T rounded to fp16
+ * (bitsmoe/models/qwen3moe/bitsmoe_block.py:63-64).  x [T, hidden] of x_dtype. */
+BM_API int bm_basis_project(const bm_layer_t* layer, const void* x, int x_dtype, int32_t T,
+                     uint16_t* h_gate, uint16_t* h_up, void* stream);
+BM_API size_t bm_experts_workspace_bytes(const bm_layer_t* layer, int32_t T, int32_t num_assign, int32_t path);
+/* The op contract of moe_packed_forward (bitsmoe/algorithms/cpp/mlp_forward_binding.cpp:53-155,
+ * bitsmoe/algorithms/cpp/mlp_forward.cu:2701-3074): rank_accum fp32 [T, rank_out] is
+ * overwritten with  sum over assignments of  route_w * s_down * (W_down . (silu(g) * u)). */
+BM_API int bm_experts_forward(const bm_layer_t* layer, const uint16_t* h_gate, const uint16_t* h_up,
+                       const int32_t* token_indices, const int32_t* expert_offsets, const float* route_weights,
+                       int32_t T, int32_t num_assign, float* rank_accum, int32_t path,
+                       void* workspace, size_t workspace_bytes, void* stream);
+/* y = fp16(rank_accum) @ U_down^T (+ residual) in y_dtype (bitsmoe/models/base_block.py:414 and the
+ * adds of qwen3moe/bitsmoe_block.py:95, deepseekv2/bitsmoe_block.py:123-124).  residual may be NULL. */
+BM_API int bm_combine_down_basis(const bm_layer_t* layer, const float* rank_accum, int32_t T,
+                          const void* residual, void* y, int y_dtype, void* stream);
+
+/* Whole block for given router logits: route -> basis -> experts -> down basis, on one
+ * stream with no host synchronisation (the forward of
+ * bitsmoe/models/qwen3moe/bitsmoe_block.py:39-98 after `router_logits = self.gate(x)`). */
+BM_API size_t bm_layer_workspace_bytes(const bm_layer_t* layer, int32_t T, int32_t k);
+BM_API int bm_layer_forward(const bm_layer_t* layer, const void* x, int x_dtype, const void* logits, int logits_dtype,
+                     int32_t T, int32_t num_routed, int32_t k, int32_t renorm, int32_t weight_round,
+                     const int32_t* global_to_local, const void* residual, void* y, int32_t path,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITSMOE_B200_H_ */

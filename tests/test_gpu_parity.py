@@ -1,0 +1,213 @@
+"""GPU parity: every stage through the C ABI against the CPU oracle, and against the
+reference's own CUDA extensions (compiled for sm_100a into oracle/_ref) when present."""
+import numpy as np
+import pytest
+import torch
+
+from bitsmoe_b200 import capi, synth
+from bitsmoe_b200.layer import PackedLayer, route_build, route_topk
+from bitsmoe_b200.quant.bitpack import BitPack
+from oracle import bitplane
+from oracle import forward as oforward
+from oracle import packer as opacker
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rand_codes(rng, bits, shape):
+    if bits == 1:
+        return (rng.integers(0, 2, size=shape) * 2 - 1).astype(np.int8)
+    return rng.integers(-(2 ** (bits - 1)), 2 ** (bits - 1), size=shape).astype(np.int8)
+
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 6, 8])
+@pytest.mark.parametrize("shape", [(1, 32), (37, 96), (64, 128), (5, 70), (300, 1408)])
+def test_bitplane_codec_bit_exact(bits, shape):
+    rng = np.random.default_rng(bits * 100 + shape[1])
+    q = _rand_codes(rng, bits, shape)
+    want = bitplane.pack_bitplanes_i8(q, bits)
+    packed, cols = BitPack.pack(torch.from_numpy(q).to(DEV), bits)
+    assert cols == shape[1]
+    got = packed.cpu().to(torch.int64).numpy().astype(np.uint32)
+    assert np.array_equal(got, want)
+    back = BitPack.unpack(packed, bits, shape[1]).cpu().numpy()
+    assert np.array_equal(back, q)
+    ref = helpers.load_reference_ext("_bitpack_cuda")
+    if ref is not None:   # the reference's own kernels, same bits
+        ref_packed = getattr(ref, f"pack_int8_{bits}bit")(torch.from_numpy(q).to(DEV))
+        assert torch.equal(ref_packed.cpu().to(torch.int64), packed.cpu().to(torch.int64))
+        ref_back = getattr(ref, f"unpack_int8_{bits}bit")(packed)[:, :shape[1]]
+        assert torch.equal(ref_back.cpu(), torch.from_numpy(q))
+
+
+def test_bitplane_errors():
+    with pytest.raises(ValueError, match="Unsupported bit width"):
+        BitPack.pack(torch.zeros(1, 32, dtype=torch.int8, device=DEV), 5)
+    with pytest.raises(TypeError):
+        BitPack.pack(torch.zeros(1, 32, dtype=torch.int32, device=DEV), 2)
+    with pytest.raises(ValueError, match="requires CUDA"):
+        BitPack.pack(torch.zeros(1, 32, dtype=torch.int8), 2)
+    out, _ = BitPack.pack(torch.zeros(0, 32, dtype=torch.int8, device=DEV), 2)
+    assert out.shape == (0, 2)
+
+
+@pytest.fixture(scope="module")
+def mixed():
+    layer = helpers.mixed_everything_layer()
+    return layer, synth.to_packed_layer(layer, DEV), helpers.decoded_experts(layer)
+
+
+@pytest.fixture(scope="module")
+def q30_small():
+    cfg = synth.LayerConfig("q30-16e", 2048, 16, 768, 4)
+    layer = synth.make_layer(cfg, seed=11, device=DEV)
+    return layer, synth.to_packed_layer(layer, DEV), helpers.decoded_experts(layer)
+
+
+def test_decoded_codes_bit_exact(mixed):
+    layer, packed, _ = mixed
+    for which, tag in enumerate(("gate", "up", "down")):
+        for e in range(layer.cfg.num_experts):
+            want = opacker.decode_matrix(helpers.table_entry(layer, tag, e), layer.cfg.intermediate)["codes"]
+            got = packed.decode_codes(e, which).cpu().numpy()
+            assert np.array_equal(got, want), (tag, e)
+
+
+@pytest.mark.parametrize("T,E,k,renorm,wdt", [(1, 128, 8, True, torch.float16), (64, 128, 8, True, torch.bfloat16),
+                                              (33, 512, 10, True, torch.float16), (7, 64, 6, False, None),
+                                              (300, 8, 2, True, torch.float16)])
+def test_route_topk(T, E, k, renorm, wdt):
+    cfg = synth.LayerConfig("r", 64, E, 128, k)
+    logits = synth.router_logits(cfg, T, seed=T + E, zipf_s=1.1 if T == 33 else 0.0)
+    want_idx, want_w = oforward.router(logits, k, renorm, wdt)
+    idx, w = route_topk(logits.to(DEV), k, renorm, wdt)
+    assert torch.equal(idx.cpu().long(), want_idx)           # no exact ties in N(0,1) logits
+    tol = 2 ** -10 if wdt is not None else 1e-6               # one rounding step of the weight dtype
+    assert torch.allclose(w.cpu(), want_w, rtol=tol, atol=1e-7)
+    # lower precision logits, and exact ties resolved to the lower expert id
+    tied = torch.zeros(3, E)
+    idx2, _ = route_topk(tied.to(DEV).half(), k, True, torch.float16)
+    assert idx2.cpu().tolist() == [list(range(k))] * 3
+
+
+@pytest.mark.parametrize("T,E,k,masked", [(1, 128, 8, False), (64, 128, 8, False), (64, 512, 10, True),
+                                          (700, 16, 4, False), (8192, 128, 8, True), (0, 8, 2, False)])
+def test_route_build_bit_exact(T, E, k, masked):
+    g = torch.Generator().manual_seed(T + E)
+    logits = torch.randn(T, E, generator=g) + torch.log(1.0 / torch.arange(1, E + 1) ** 1.1)
+    idx, w = oforward.router(logits, k, True, torch.float16) if T else (torch.zeros(0, k, dtype=torch.long), torch.zeros(0, k))
+    g2l, n_local = None, E
+    if masked:   # three "super" experts are not packed: their assignments drop out
+        g2l = torch.arange(E, dtype=torch.int32)
+        g2l[[1, 5, 9]] = -1
+        g2l[g2l >= 0] = torch.arange(E - 3, dtype=torch.int32)
+        n_local = E - 3
+    want_tok, want_off, want_w = oforward.build_routing(idx, w, n_local, g2l)
+    tok, off, rw, tiles, counts = route_build(idx.to(DEV), w.to(DEV), n_local, None if g2l is None else g2l.to(DEV))
+    n = int(want_off[-1])
+    assert torch.equal(off.cpu(), want_off)
+    assert counts.cpu().tolist()[0] == n
+    assert torch.equal(tok.cpu()[:n], want_tok)
+    assert torch.equal(rw.cpu()[:n], want_w)
+    # tile table: every expert's rows covered once, in order, in tiles of <= 128
+    tt = tiles.cpu()[: int(counts.cpu()[1])].tolist()
+    cover = []
+    for e, a0, rows in tt:
+        assert 1 <= rows <= 128
+        cover.extend(range(a0, a0 + rows))
+        assert want_off[e] <= a0 and a0 + rows <= want_off[e + 1]
+    assert cover == list(range(n))
+    assert all(r[2] == 0 for r in tiles.cpu()[int(counts.cpu()[1]):].tolist())
+
+
+def _inputs(layer, T, seed):
+    cfg = layer.cfg
+    x = synth.activations(cfg, T, seed=seed)
+    logits = synth.router_logits(cfg, T, seed=seed + 1)
+    return x, logits
+
+
+@pytest.mark.parametrize("T", [1, 3, 17])
+def test_experts_forward_all_widths_vs_oracle(mixed, T):
+    layer, packed, experts = mixed
+    x, logits = _inputs(layer, T, 20 + T)
+    o = oforward.layer_forward(x, logits, layer.vh_gate, layer.vh_up, layer.u_down, experts, layer.cfg.top_k)
+    got = packed.experts_forward(o["h_gate"].to(DEV), o["h_up"].to(DEV), o["token_indices"].to(DEV),
+                                 o["expert_offsets"].to(DEV), o["route_flat"].to(DEV), path=capi.PATH_GENERIC)
+    helpers.assert_close(got, o["rank_accum"], rtol=1e-3, atol=1e-5, what="rank_accum (generic path)")
+
+
+@pytest.mark.parametrize("T", [1, 8, 64, 200])
+def test_experts_forward_q30_shape_vs_oracle_and_reference(q30_small, T):
+    layer, packed, experts = q30_small
+    x, logits = _inputs(layer, T, 40 + T)
+    o = oforward.layer_forward(x, logits, layer.vh_gate.cpu(), layer.vh_up.cpu(), layer.u_down.cpu(), experts,
+                               layer.cfg.top_k)
+    args = [o[k].to(DEV) for k in ("h_gate", "h_up", "token_indices", "expert_offsets", "route_flat")]
+    got = packed.experts_forward(*args, path=capi.PATH_GENERIC)
+    helpers.assert_close(got, o["rank_accum"], rtol=1e-3, atol=1e-5, what="rank_accum vs fp32 oracle")
+    ref = helpers.load_reference_ext("_mlp_forward_cuda")
+    if ref is not None:
+        want = ref.moe_packed_forward(*args, *helpers.ref_args(layer, DEV), layer.cfg.rank, layer.cfg.intermediate, 0)
+        helpers.assert_close(got, want, what="rank_accum vs the reference's kernels")
+        helpers.assert_close(want, o["rank_accum"], what="reference kernels vs fp32 oracle")
+
+
+def test_op_shim_matches_reference_contract(q30_small):
+    from bitsmoe_b200.algorithms import _HAS_MLP_FORWARD_CUDA, mlp_forward_cuda
+    assert _HAS_MLP_FORWARD_CUDA
+    layer, packed, experts = q30_small
+    x, logits = _inputs(layer, 5, 77)
+    o = oforward.layer_forward(x, logits, layer.vh_gate.cpu(), layer.vh_up.cpu(), layer.u_down.cpu(), experts,
+                               layer.cfg.top_k)
+    args = [o[k].to(DEV) for k in ("h_gate", "h_up", "token_indices", "expert_offsets", "route_flat")]
+    lists = helpers.ref_args(layer, DEV)
+    got = mlp_forward_cuda.moe_packed_forward(*args, *lists, layer.cfg.rank, layer.cfg.intermediate, 0)
+    assert got.dtype == torch.float32 and tuple(got.shape) == (5, layer.cfg.rank)
+    helpers.assert_close(got, o["rank_accum"], rtol=1e-3, atol=1e-5, what="op shim")
+    empty = mlp_forward_cuda.moe_packed_forward(args[0], args[1], args[2][:0], args[3], args[4][:0], *lists,
+                                                layer.cfg.rank, layer.cfg.intermediate, 0)
+    assert float(empty.abs().max()) == 0.0
+    with pytest.raises(RuntimeError, match="h_gate must be float16"):
+        mlp_forward_cuda.moe_packed_forward(args[0].float(), *args[1:], *lists, layer.cfg.rank, layer.cfg.intermediate, 0)
+    with pytest.raises(RuntimeError, match="only SiLU"):
+        mlp_forward_cuda.moe_packed_forward(*args, *lists, layer.cfg.rank, layer.cfg.intermediate, 1)
+    with pytest.raises(RuntimeError, match="gate_scale size mismatch"):
+        bad = list(lists)
+        bad[4] = bad[4][:-1]
+        mlp_forward_cuda.moe_packed_forward(*args, *bad, layer.cfg.rank, layer.cfg.intermediate, 0)
+
+
+@pytest.mark.parametrize("T,dtype", [(1, torch.bfloat16), (8, torch.float16), (64, torch.bfloat16), (300, torch.bfloat16)])
+def test_layer_forward_vs_oracle(q30_small, T, dtype):
+    layer, packed, experts = q30_small
+    cfg = layer.cfg
+    x = synth.activations(cfg, T, seed=5, dtype=dtype)
+    logits = synth.router_logits(cfg, T, seed=6)
+    o = oforward.layer_forward(x, logits, layer.vh_gate.cpu(), layer.vh_up.cpu(), layer.u_down.cpu(), experts, cfg.top_k,
+                               weight_dtype=dtype)
+    y = packed.forward(x.to(DEV), logits.to(DEV), cfg.top_k, True, dtype)
+    assert y.dtype == dtype
+    helpers.assert_close(y, o["y_fp32"], what=f"layer output T={T}")
+    hg, hu = packed.basis_project(x.to(DEV))
+    helpers.assert_close(hg, o["h_gate"], rtol=2e-3, atol=2e-3, what="h_gate")
+    # residual (shared expert / dense experts) is added inside the last kernel
+    res = torch.randn(T, cfg.hidden).to(dtype)
+    y2 = packed.forward(x.to(DEV), logits.to(DEV), cfg.top_k, True, dtype, residual=res.to(DEV))
+    helpers.assert_close(y2, o["y_fp32"] + res.float(), what="layer output + residual")
+
+
+def test_layer_rejects_bad_meta(mixed):
+    layer, _, _ = mixed
+    t = {tag: {f: [x.clone().to(DEV) for x in v] for f, v in fields.items()} for tag, fields in layer.tables.items()}
+    t["up"]["tile_meta"][1][0, 0] = 10 ** 8          # payload offset beyond the buffer
+    with pytest.raises(capi.BitsMoEError, match="payload"):
+        PackedLayer(t["gate"], t["up"], t["down"], layer.cfg.intermediate, layer.cfg.rank, layer.vh_gate.to(DEV),
+                    layer.vh_up.to(DEV), layer.u_down.to(DEV))
+    t["up"]["tile_meta"][1][0, 0] = 0
+    t["down"]["slab_meta"][0][0, 0] = 5              # unsupported width
+    with pytest.raises(capi.BitsMoEError, match="Unsupported bits=5"):
+        PackedLayer(t["gate"], t["up"], t["down"], layer.cfg.intermediate, layer.cfg.rank, layer.vh_gate.to(DEV),
+                    layer.vh_up.to(DEV), layer.u_down.to(DEV))
