@@ -98,7 +98,6 @@ def test_qwen3next_block_adds_gated_shared_expert():
     o = oforward.layer_forward(x.reshape(10, -1), logits.float().cpu(), layer.vh_gate, layer.vh_up, layer.u_down, experts,
                                cfg.top_k, True, torch.bfloat16, shared=layer.shared)
     helpers.assert_close(y.reshape(10, -1), o["y_fp32"], what="Qwen3-Next block")
-    assert blk.shared_vh_gate_proj.dtype == torch.float16      # the basis stays fp16 whatever the model dtype
 
 
 class StubMoEGate(nn.Module):
