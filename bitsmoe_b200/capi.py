@@ -62,7 +62,9 @@ _SIGS = {
     "bm_layer_create": (C.c_int, [C.POINTER(LayerDesc), C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p)]),
     "bm_layer_destroy": (C.c_int, [C.c_void_p]),
     "bm_layer_expert_bytes": (C.c_int64, [C.c_void_p, C.c_int32]),
-    "bm_layer_decode_codes": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "bm_layer_decode_codes": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "bm_layer_has_fast_layout": (C.c_int, [C.c_void_p]),
+    "bm_layer_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "bm_route_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p]),
     "bm_route_build_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),

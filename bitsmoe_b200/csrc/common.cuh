@@ -71,6 +71,37 @@ struct MatHost {
   int32_t n_rows = 0;
 };
 
+constexpr int FAST_MAX_TOK = 16;   // assignments per pass of the decode kernel
+
+struct FastMat {
+  int32_t nblk[3];      // 16-slot blocks holding 4-, 3-, 2-bit rows
+  int32_t nslots;       // 16 * total blocks
+  int32_t words;        // uint32 words per tile = 64 * (4 nblk[0] + 3 nblk[1] + 2 nblk[2])
+  int32_t tab_off;      // byte offset (from arena base) of [int16 rank[nslots] | fp16 s[nslots] | int16 row[nslots]]
+  int32_t pad_[2];
+};
+
+struct FastExpert {
+  FastMat m[3];
+  int64_t unit_base;    // byte offset of tile 0's unit block from arena base
+  int32_t unit_bytes;   // bytes per unit block (multiple of 128)
+  int32_t sec_off[6];   // byte offsets inside a unit: scale g,u,d then words g,u,d
+  int32_t pad_;
+};
+
+struct FastPlan {
+  bool ok = false;
+  std::vector<FastExpert> experts;
+  std::vector<int16_t> slot_row;      // concatenated per (expert, matrix): slot -> local row or -1
+  std::vector<int32_t> slot_row_off;  // [E*3] element offset into slot_row
+  size_t table_off = 0;               // FastExpert table
+  size_t tabs_off = 0;                // per-matrix rank/s/row tables
+  size_t units_off = 0;
+  size_t total = 0;
+  int max_unit_bytes = 0, max_slots = 0;
+  int* status_dev = nullptr;       // device flag set by a kernel whose bounded wait gave up
+};
+
 __host__ __device__ inline int words_per_row(int bits) { return bits == 16 ? 16 : bits; }
 
 __host__ __device__ inline int code_offset(int bits) {
@@ -104,6 +135,7 @@ struct GemmArgs {
 };
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+__host__ __device__ inline size_t align_up_c(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace bm
 
@@ -119,5 +151,9 @@ struct bm_layer {
   bm::ExpertDev* experts_dev = nullptr;  // in the arena
   void* arena = nullptr;
   size_t arena_bytes = 0;
-  bool fast_ok = false;            // every slab is 2/3/4-bit and shapes fit the tensor / decode paths
+  bool fast_ok = false;            // every slab is 2/3/4-bit and shapes fit the decode / tensor paths
+  const bm::FastExpert* fast_dev = nullptr;   // in the arena
+  std::vector<bm::FastExpert> fast_host;
+  int max_unit_bytes = 0, max_slots = 0;
+  int* status_dev = nullptr;       // device flag set by a kernel whose bounded wait gave up
 };

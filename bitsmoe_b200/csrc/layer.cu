@@ -20,6 +20,12 @@ int set_error(int status, const char* fmt, ...) {
 
 // from the other translation units
 int launch_gemm_nt(const GemmArgs& g, int problems, cudaStream_t st);
+void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P);
+int build_fast(bm_layer* L, const FastPlan& P, cudaStream_t st);
+size_t fast_build_scratch_bytes(const FastPlan& P);
+int launch_arena_decode(const bm_layer* L, int e, int w, int8_t* codes, cudaStream_t st);
+int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
+                          const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
 int launch_experts_generic(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                            const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum,
                            cudaStream_t st);
@@ -93,8 +99,15 @@ static int check_desc(const bm_layer_desc_t* d) {
   return BM_OK;
 }
 
-static size_t arena_need(const bm_layer_desc_t* d) {
-  return align_up(sizeof(ExpertDev) * static_cast<size_t>(d->num_experts > 0 ? d->num_experts : 1), 256);
+// arena = [ExpertDev table][status flag][arena layout ...][build scratch]
+static size_t table_bytes(int num_experts) {
+  return align_up(sizeof(ExpertDev) * static_cast<size_t>(num_experts > 0 ? num_experts : 1), 256);
+}
+static size_t base_bytes(int num_experts) { return table_bytes(num_experts) + 256; }
+
+static size_t arena_need(const bm_layer* L, FastPlan* P) {
+  plan_fast(L, base_bytes(L->num_experts), P);
+  return P->ok ? P->total + fast_build_scratch_bytes(*P) : base_bytes(L->num_experts);
 }
 
 static int build_host(const bm_layer_desc_t* d, bm_layer* L) {
@@ -232,7 +245,8 @@ extern "C" int bm_layer_plan(const bm_layer_desc_t* desc, size_t* arena_bytes) {
   bm_layer tmp;
   const int rc = build_host(desc, &tmp);
   if (rc) return rc;
-  *arena_bytes = arena_need(desc);
+  FastPlan P;
+  *arena_bytes = arena_need(&tmp, &P);
   return BM_OK;
 }
 
@@ -244,7 +258,8 @@ extern "C" int bm_layer_create(const bm_layer_desc_t* desc, void* arena, size_t 
   BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "out of host memory");
   int rc = build_host(desc, L);
   if (rc) { delete L; return rc; }
-  const size_t need = arena_need(desc);
+  FastPlan P;
+  const size_t need = arena_need(L, &P);
   if (arena == nullptr || arena_bytes < need || (reinterpret_cast<uintptr_t>(arena) & 255u)) {
     delete L;
     return set_error(BM_ERR_WORKSPACE, "layer arena must be 256-byte aligned and hold %zu bytes (%zu given)", need, arena_bytes);
@@ -260,13 +275,23 @@ extern "C" int bm_layer_create(const bm_layer_desc_t* desc, void* arena, size_t 
     tab[e].m[2] = to_dev(desc->down[e]);
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (desc->num_experts) {
-    cudaError_t e = cudaMemcpyAsync(L->experts_dev, tab.data(), sizeof(ExpertDev) * tab.size(), cudaMemcpyHostToDevice, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) {
-      delete L;
-      return set_error(BM_ERR_CUDA, "uploading the expert table failed: %s", cudaGetErrorString(e));
-    }
+  L->status_dev = reinterpret_cast<int*>(static_cast<unsigned char*>(arena) + table_bytes(desc->num_experts));
+  cudaError_t ce = cudaMemsetAsync(L->status_dev, 0, 256, st);
+  if (ce == cudaSuccess && desc->num_experts)
+    ce = cudaMemcpyAsync(L->experts_dev, tab.data(), sizeof(ExpertDev) * tab.size(), cudaMemcpyHostToDevice, st);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+  if (ce != cudaSuccess) {
+    delete L;
+    return set_error(BM_ERR_CUDA, "uploading the expert table failed: %s", cudaGetErrorString(ce));
+  }
+  if (P.ok) {
+    L->fast_host = P.experts;
+    L->fast_dev = reinterpret_cast<const FastExpert*>(static_cast<unsigned char*>(arena) + P.table_off);
+    L->max_unit_bytes = P.max_unit_bytes;
+    L->max_slots = P.max_slots;
+    rc = build_fast(L, P, st);
+    if (rc) { delete L; return rc; }
+    L->fast_ok = true;
   }
   *out = L;
   return BM_OK;
@@ -282,9 +307,29 @@ extern "C" int64_t bm_layer_expert_bytes(const bm_layer_t* L, int32_t e) {
   return L->host[0][e].bytes + L->host[1][e].bytes + L->host[2][e].bytes;
 }
 
-extern "C" int bm_layer_decode_codes(const bm_layer_t* L, int32_t e, int32_t which, int8_t* codes, void* stream) {
+extern "C" int bm_layer_has_fast_layout(const bm_layer_t* L) { return L && L->fast_ok ? 1 : 0; }
+
+extern "C" int bm_layer_status(const bm_layer_t* L, void* stream) {
+  BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "layer_status: null layer");
+  int flag = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BM_CUDA(cudaMemcpyAsync(&flag, L->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
+  BM_CUDA(cudaStreamSynchronize(st));
+  if (flag != 0) {
+    BM_CUDA(cudaMemsetAsync(L->status_dev, 0, sizeof(int), st));
+    return set_error(BM_ERR_TIMEOUT, "a kernel of this layer gave up a bounded wait; its outputs are undefined");
+  }
+  return BM_OK;
+}
+
+extern "C" int bm_layer_decode_codes(const bm_layer_t* L, int32_t e, int32_t which, int32_t source, int8_t* codes,
+                                     void* stream) {
   BM_REQUIRE(L && codes, BM_ERR_INVALID_ARG, "decode_codes: null pointer");
   BM_REQUIRE(e >= 0 && e < L->num_experts && which >= 0 && which < 3, BM_ERR_INVALID_ARG, "decode_codes: bad index");
+  if (source == 1) {
+    BM_REQUIRE(L->fast_ok, BM_ERR_UNSUPPORTED, "decode_codes: this layer has no arena layout");
+    return launch_arena_decode(L, e, which, codes, static_cast<cudaStream_t>(stream));
+  }
   const MatDev md = to_dev(L->src[which][e]);
   const int64_t total = static_cast<int64_t>(md.n_rows) * L->intermediate;
   if (total == 0) return BM_OK;
@@ -337,8 +382,12 @@ extern "C" int bm_experts_forward(const bm_layer_t* L, const uint16_t* h_gate, c
   if (num_assign == 0 || L->num_experts == 0) return BM_OK;
   BM_REQUIRE(h_gate && h_up && token_indices && expert_offsets && route_weights, BM_ERR_INVALID_ARG,
              "experts_forward: null pointer");
-  BM_REQUIRE(path == BM_PATH_AUTO || path == BM_PATH_GENERIC, BM_ERR_UNSUPPORTED,
-             "experts_forward: path %d is not available for this layer", path);
+  BM_REQUIRE(path != BM_PATH_TENSOR, BM_ERR_UNSUPPORTED, "experts_forward: the tensor path is not available");
+  BM_REQUIRE(path != BM_PATH_DECODE || L->fast_ok, BM_ERR_UNSUPPORTED,
+             "experts_forward: the decode path needs 2/3/4-bit rows and full tiles; this layer has neither");
+  if (L->fast_ok && path != BM_PATH_GENERIC)
+    return launch_experts_decode(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
+                                 token_indices, expert_offsets, route_weights, T, rank_accum, st);
   return launch_experts_generic(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
                                 token_indices, expert_offsets, route_weights, T, rank_accum, st);
 }

@@ -124,11 +124,21 @@ class PackedLayer:
     def expert_bytes(self, e: int) -> int:
         return int(capi.lib().bm_layer_expert_bytes(self._handle, e))
 
-    def decode_codes(self, e: int, which: int) -> torch.Tensor:
+    @property
+    def has_fast_layout(self) -> bool:
+        return bool(capi.lib().bm_layer_has_fast_layout(self._handle))
+
+    def check_status(self) -> None:
+        """Synchronises and raises if a kernel of this layer gave up a bounded device-side wait."""
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().bm_layer_status(self._handle, capi.stream_ptr(self.device)))
+
+    def decode_codes(self, e: int, which: int, source: int = 0) -> torch.Tensor:
+        """int8 codes [stored rows, intermediate]; source 0 = reference buffers, 1 = repacked arena."""
         n_rows = self._keep[which * self.num_experts + e]["rank_idx"].numel()
         out = torch.empty((n_rows, self.intermediate_size), dtype=torch.int8, device=self.device)
         with torch.cuda.device(self.device):
-            capi.check(capi.lib().bm_layer_decode_codes(self._handle, e, which, out.data_ptr(),
+            capi.check(capi.lib().bm_layer_decode_codes(self._handle, e, which, source, out.data_ptr(),
                                                         capi.stream_ptr(self.device)))
         return out
 

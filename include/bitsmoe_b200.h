@@ -97,9 +97,18 @@ BM_API int bm_layer_destroy(bm_layer_t* layer);
 /* Bytes the forward path reads for the experts, as stored by the reference
  * (payload + scale + s + rank_idx + meta of the three matrices of expert e). */
 BM_API int64_t bm_layer_expert_bytes(const bm_layer_t* layer, int32_t expert);
-/* Decoded integer codes of one matrix through the arena (repacked) layout:
- * int8 [n_rows, intermediate], local-row order.  For the bit-exactness tests. */
-BM_API int bm_layer_decode_codes(const bm_layer_t* layer, int32_t expert, int32_t which, int8_t* codes, void* stream);
+/* Decoded integer codes of one matrix, int8 [n_rows, intermediate] in stored (local) row order,
+ * read either from the reference buffers in place (source 0; the decode of
+ * bitsmoe/algorithms/cpp/mlp_forward.cu:203-275) or back out of the repacked arena (source 1;
+ * BM_ERR_UNSUPPORTED when the layer has no arena layout).  For the bit-exactness tests. */
+BM_API int bm_layer_decode_codes(const bm_layer_t* layer, int32_t expert, int32_t which, int32_t source, int8_t* codes,
+                                 void* stream);
+/* 1 when the layer was repacked into the arena layout that the decode and tensor paths need
+ * (every stored row 2, 3 or 4 bits wide, full tiles), else 0. */
+BM_API int bm_layer_has_fast_layout(const bm_layer_t* layer);
+/* Synchronises `stream` and reports whether any kernel of this layer gave up a bounded wait since
+ * the last call (BM_ERR_TIMEOUT) -- the device-side counterpart of C10_CUDA_KERNEL_LAUNCH_CHECK. */
+BM_API int bm_layer_status(const bm_layer_t* layer, void* stream);
 
 /* ---- routing -----------------------------------------------------------
  * Router tail of bitsmoe/models/qwen3moe/bitsmoe_block.py:47-51 (softmax in
