@@ -22,7 +22,7 @@ INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
-]
+] + os.environ.get("BM_EXTRA_NVCC_FLAGS", "").split()
 
 
 def sources():

@@ -62,7 +62,8 @@ void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P) {
   }
   P->total = align_up(off, 256);
   // a unit block plus activation staging has to fit one CTA's shared memory
-  P->ok = P->max_unit_bytes + 2 * FAST_MAX_TOK * P->max_slots * 2 + 8192 <= 200 * 1024;
+  P->ok = 2 * (P->max_unit_bytes + 3 * (P->max_slots * 6 + 16) + 2 * FAST_MAX_TOK * L->rank_in * 2) +
+              2 * FAST_MAX_TOK * (P->max_slots + 8) * 2 + 8192 <= 200 * 1024 && L->rank_in % 8 == 0;
 }
 
 __device__ __forceinline__ int source_bit(const MatDev& md, int row, int col_in_tile, int tile, int plane, int* bits_out) {

@@ -71,7 +71,7 @@ struct MatHost {
   int32_t n_rows = 0;
 };
 
-constexpr int FAST_MAX_TOK = 16;   // assignments per pass of the decode kernel
+constexpr int FAST_MAX_TOK = 8;    // assignments per pass of the decode kernel (one MMA N-block)
 
 struct FastMat {
   int32_t nblk[3];      // 16-slot blocks holding 4-, 3-, 2-bit rows

@@ -15,7 +15,22 @@
 
 namespace bm {
 
-constexpr int DEC_THREADS = 256;
+// Optional phase timing (debug builds only): cycles of compute-warp 0, accumulated into status[8 + phase].
+#ifdef BM_DECODE_TIMING
+#define BM_TICK(phase)                                                                   \
+  do {                                                                                   \
+    if (threadIdx.x == 0) {                                                              \
+      const long long now_ = clock64();                                                  \
+      atomicAdd(reinterpret_cast<unsigned long long*>(bm_timing_base) + (phase), static_cast<unsigned long long>(now_ - bm_tick_)); \
+      bm_tick_ = now_;                                                                   \
+    }                                                                                    \
+  } while (0)
+#else
+#define BM_TICK(phase) do {} while (0)
+#endif
+
+constexpr int DEC_THREADS = 288;            // 8 compute warps + 1 producer warp
+constexpr int DEC_MAX_E = 1024;
 constexpr uint32_t DEC_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -71,11 +86,18 @@ __device__ __forceinline__ void planes_to_afrag(const uint32_t* __restrict__ w, 
 // One group of slot blocks of uniform width.  `words` points at the group's first word for this warp's
 // operand-row block; consecutive contraction blocks are `stride_kb` words apart; `bfrag` points at the
 // B operand row (assignment g of N-block 0) at the first contraction position of the group.
+// `off_acc` accumulates the same products against a constant A fragment whose every code is the
+// group's offset 2^(BITS-1): after the loop its column n holds offset * sum_k B[k][n] (times 2^-24),
+// the term that turns sum u*B into sum q*B.
 template <int BITS, int NB>
 __device__ __forceinline__ void mma_group(const uint32_t* __restrict__ words, int stride_kb, int nkb, int g, int t,
-                                          const __half* __restrict__ bop, int b_stride, float (&acc)[2][4]) {
+                                          const __half* __restrict__ bop, int b_stride, float (&acc)[2][4],
+                                          float (&off_acc)[2][4]) {
   const uint32_t* wp = words + g * BITS;
   const __half* bp = bop + static_cast<size_t>(g) * b_stride + 2 * t;
+  constexpr uint32_t kOff = (1u << (BITS - 1)) * 0x00010001u;
+  const uint32_t offs[4] = {kOff, kOff, kOff, kOff};
+#pragma unroll 2
   for (int kb = 0; kb < nkb; ++kb) {
     uint32_t w[BITS];
 #pragma unroll
@@ -85,7 +107,9 @@ __device__ __forceinline__ void mma_group(const uint32_t* __restrict__ words, in
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
       const __half* b = bp + static_cast<size_t>(nb) * 8 * b_stride;
-      mma_16816(acc[nb], a, *reinterpret_cast<const uint32_t*>(b), *reinterpret_cast<const uint32_t*>(b + 8));
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(b), b1 = *reinterpret_cast<const uint32_t*>(b + 8);
+      mma_16816(acc[nb], a, b0, b1);
+      mma_16816(off_acc[nb], offs, b0, b1);
     }
     wp += stride_kb;
     bp += 16;
@@ -93,253 +117,348 @@ __device__ __forceinline__ void mma_group(const uint32_t* __restrict__ words, in
 }
 
 struct DecSmem {
-  unsigned char* unit;
-  __half* actp;     // [2][FAST_MAX_TOK][slots_stride]
-  __half* zp;       // [FAST_MAX_TOK][N_TILE + 8]
-  float* corr;      // [3][FAST_MAX_TOK]
-  int* tok;         // [FAST_MAX_TOK]
-  float* rw;        // [FAST_MAX_TOK]
-  uint64_t* bar;    // [2]
+  unsigned char* unit;         // current unit block
+  const unsigned char* tabs;   // current expert's slot tables (copy of the arena region starting at tab_base)
+  int tab_base;                // arena offset the copy starts at
+  __half* actp;                // [2][FAST_MAX_TOK][slots_stride]
+  __half* zp;                  // [FAST_MAX_TOK][N_TILE + 8]
+  int* tok;                    // [FAST_MAX_TOK]
+  float* rw;                   // [FAST_MAX_TOK]
 };
+
+constexpr int DEC_CONSUMERS = 256;            // 8 compute warps; warp 8 is the producer
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(DEC_CONSUMERS) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
 
 constexpr int ZP_STRIDE = N_TILE + 8;   // halves; +8 keeps the B-fragment loads of 8 rows on distinct banks
 
 __host__ __device__ inline int dec_slots_stride(int max_slots) { return max_slots + 8; }
 
-__host__ __device__ inline size_t dec_smem_bytes(int max_unit_bytes, int max_slots) {
-  size_t o = align_up_c(static_cast<size_t>(max_unit_bytes), 128);
+// One pipeline stage: [unit block | per-expert slot tables | h rows of the first pass's tokens (gate, up)]
+__host__ __device__ inline size_t dec_stage_bytes(int max_unit_bytes, int max_slots, int h_rank) {
+  return align_up_c(static_cast<size_t>(max_unit_bytes), 128) + align_up_c(static_cast<size_t>(3) * (max_slots * 6 + 16), 128) +
+         align_up_c(static_cast<size_t>(2) * FAST_MAX_TOK * h_rank * 2, 128);
+}
+
+__host__ __device__ inline size_t dec_smem_bytes(int max_unit_bytes, int max_slots, int h_rank) {
+  size_t o = 2 * dec_stage_bytes(max_unit_bytes, max_slots, h_rank);
   o += static_cast<size_t>(2) * FAST_MAX_TOK * dec_slots_stride(max_slots) * 2;
   o += static_cast<size_t>(FAST_MAX_TOK) * ZP_STRIDE * 2;
-  o += 3 * FAST_MAX_TOK * 4 + FAST_MAX_TOK * 4 + FAST_MAX_TOK * 4 + 64;
+  o += DEC_MAX_E * 2;
   return align_up_c(o, 128);
 }
 
 template <int NB>
 __device__ __forceinline__ void decode_pass(const FastExpert& fe, const DecSmem& sm, int slots_stride, int tile, int n_valid,
                                             int npass, int rank_out, float* __restrict__ rank_accum,
-                                            const unsigned char* __restrict__ arena, bool first_pass, bool* ok) {
+                                            const unsigned char* __restrict__ arena, uint64_t* bar_down, uint32_t parity,
+                                            bool* ok, long long& bm_tick_, int* bm_timing_base) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   // ---- gate / up: this warp owns columns 16*warp .. 16*warp+15 of the tile
-  float acc[2][2][4];
+  float acc[2][2][4], offa[2][2][4];
 #pragma unroll
   for (int m = 0; m < 2; ++m)
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[m][nb][j] = 0.f;
+      for (int j = 0; j < 4; ++j) acc[m][nb][j] = offa[m][nb][j] = 0.f;
 #pragma unroll
   for (int m = 0; m < 2; ++m) {
     const FastMat& fm = fe.m[m];
-    const uint32_t* words = reinterpret_cast<const uint32_t*>(sm.unit + fe.sec_off[3 + m]) + warp * 8 * 4;
+    const uint32_t* sec = reinterpret_cast<const uint32_t*>(sm.unit + fe.sec_off[3 + m]);
     const __half* bop = sm.actp + static_cast<size_t>(m) * FAST_MAX_TOK * slots_stride;
     // [kb][mblock][g][plane]: a contraction block holds 64*b words, this warp's rows start at warp*8*b
-    mma_group<4, NB>(words, 64 * 4, fm.nblk[0], g, t, bop, slots_stride, acc[m]);
-    words = words - warp * 8 * 4 + fm.nblk[0] * 64 * 4 + warp * 8 * 3;
+    mma_group<4, NB>(sec + warp * 8 * 4, 64 * 4, fm.nblk[0], g, t, bop, slots_stride, acc[m], offa[m]);
+    sec += fm.nblk[0] * 64 * 4;
     bop += fm.nblk[0] * 16;
-    mma_group<3, NB>(words, 64 * 3, fm.nblk[1], g, t, bop, slots_stride, acc[m]);
-    words = words - warp * 8 * 3 + fm.nblk[1] * 64 * 3 + warp * 8 * 2;
+    mma_group<3, NB>(sec + warp * 8 * 3, 64 * 3, fm.nblk[1], g, t, bop, slots_stride, acc[m], offa[m]);
+    sec += fm.nblk[1] * 64 * 3;
     bop += fm.nblk[1] * 16;
-    mma_group<2, NB>(words, 64 * 2, fm.nblk[2], g, t, bop, slots_stride, acc[m]);
+    mma_group<2, NB>(sec + warp * 8 * 2, 64 * 2, fm.nblk[2], g, t, bop, slots_stride, acc[m], offa[m]);
   }
-  // ---- z = silu(g) * u, written as the down product's B operand; per-token sum of z for the offset term
-  float zs[NB][2];
+  BM_TICK(3);
+  // ---- z = silu(g) * u, written as the down product's B operand
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) {
-    zs[nb][0] = zs[nb][1] = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int c = 16 * warp + g + (j >= 2 ? 8 : 0);
       const int n = nb * 8 + 2 * t + (j & 1);
-      const float gv = acc[0][nb][j] * 16777216.f - sm.corr[n];
-      const float uv = acc[1][nb][j] * 16777216.f - sm.corr[FAST_MAX_TOK + n];
+      const float gv = (acc[0][nb][j] - offa[0][nb][j]) * 16777216.f;
+      const float uv = (acc[1][nb][j] - offa[1][nb][j]) * 16777216.f;
       const float z = (c < n_valid && n < npass) ? (gv / (1.f + __expf(-gv))) * uv : 0.f;
-      const __half zh = __float2half_rn(z);
-      sm.zp[n * ZP_STRIDE + (c & ~15) + kperm16(c & 15)] = zh;
-      zs[nb][j & 1] += __half2float(zh);
+      sm.zp[n * ZP_STRIDE + (c & ~15) + kperm16(c & 15)] = __float2half_rn(z);
     }
   }
-#pragma unroll
-  for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float v = zs[nb][h];
-      v += __shfl_xor_sync(0xffffffffu, v, 4);
-      v += __shfl_xor_sync(0xffffffffu, v, 8);
-      v += __shfl_xor_sync(0xffffffffu, v, 16);
-      if (g == 0) atomicAdd(&sm.corr[2 * FAST_MAX_TOK + nb * 8 + 2 * t + h], v);
-    }
-  __syncthreads();
-  if (first_pass && !mbar_wait(&sm.bar[1], 0)) { *ok = false; return; }
+  consumer_sync();
+  BM_TICK(4);
+  if (!mbar_wait(bar_down, parity)) { *ok = false; return; }
+  BM_TICK(5);
   // ---- down: slot blocks round-robin over the warps, contraction over the tile's 128 columns
   const FastMat& fd = fe.m[2];
   const uint32_t* dwords = reinterpret_cast<const uint32_t*>(sm.unit + fe.sec_off[5]);
   const __half* scale_d = reinterpret_cast<const __half*>(sm.unit + fe.sec_off[2]);
-  const int16_t* rank_d = reinterpret_cast<const int16_t*>(arena + fd.tab_off);
-  const __half* s_d = reinterpret_cast<const __half*>(arena + fd.tab_off + fd.nslots * 2);
+  const int16_t* rank_d = reinterpret_cast<const int16_t*>(sm.tabs + (fd.tab_off - sm.tab_base));
+  const __half* s_d = reinterpret_cast<const __half*>(sm.tabs + (fd.tab_off - sm.tab_base) + fd.nslots * 2);
   const int nblk_total = fd.nslots >> 4;
   for (int mb = warp; mb < nblk_total; mb += 8) {
-    float dacc[2][4];
+    float dacc[2][4], doff[2][4];
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) dacc[nb][j] = 0.f;
-    int bits;
+      for (int j = 0; j < 4; ++j) dacc[nb][j] = doff[nb][j] = 0.f;
     if (mb < fd.nblk[0]) {
-      bits = 4;
-      mma_group<4, NB>(dwords + mb * 64 * 4, 8 * 4, 8, g, t, sm.zp, ZP_STRIDE, dacc);
+      mma_group<4, NB>(dwords + mb * 64 * 4, 8 * 4, 8, g, t, sm.zp, ZP_STRIDE, dacc, doff);
     } else if (mb < fd.nblk[0] + fd.nblk[1]) {
-      bits = 3;
-      mma_group<3, NB>(dwords + fd.nblk[0] * 64 * 4 + (mb - fd.nblk[0]) * 64 * 3, 8 * 3, 8, g, t, sm.zp, ZP_STRIDE, dacc);
+      mma_group<3, NB>(dwords + fd.nblk[0] * 64 * 4 + (mb - fd.nblk[0]) * 64 * 3, 8 * 3, 8, g, t, sm.zp, ZP_STRIDE, dacc, doff);
     } else {
-      bits = 2;
       mma_group<2, NB>(dwords + fd.nblk[0] * 64 * 4 + fd.nblk[1] * 64 * 3 + (mb - fd.nblk[0] - fd.nblk[1]) * 64 * 2, 8 * 2, 8, g,
-                       t, sm.zp, ZP_STRIDE, dacc);
+                       t, sm.zp, ZP_STRIDE, dacc, doff);
     }
-    const float off = static_cast<float>(1 << (bits - 1));
 #pragma unroll
     for (int half_rows = 0; half_rows < 2; ++half_rows) {
       const int slot = mb * 16 + g + 8 * half_rows;
       const int rk = rank_d[slot];
       if (rk < 0 || rk >= rank_out) continue;
-      const float f = __half2float(s_d[slot]) * __half2float(scale_d[slot]);
+      const float f = __half2float(s_d[slot]) * __half2float(scale_d[slot]) * 16777216.f;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int n = nb * 8 + 2 * t + h;
           if (n >= npass) continue;
-          const float v = (dacc[nb][2 * half_rows + h] * 16777216.f - off * sm.corr[2 * FAST_MAX_TOK + n]) * f * sm.rw[n];
+          const float v = (dacc[nb][2 * half_rows + h] - doff[nb][2 * half_rows + h]) * f * sm.rw[n];
           atomicAdd(&rank_accum[static_cast<int64_t>(sm.tok[n]) * rank_out + rk], v);
         }
     }
   }
 }
 
+// Persistent kernel.  Every CTA first compacts the list of experts that received tokens (from
+// expert_offsets), then walks the (active expert, tile) units u = blockIdx.x, blockIdx.x + gridDim.x, ...
+// Warp 8 is the producer: for each unit it waits until the target stage is released, fetches the expert
+// descriptor and the first pass's token ids / route weights, and starts bulk copies of the unit block, the
+// expert's slot tables and the tokens' h rows into one of two shared-memory stages; the 8 compute warps
+// consume stage `it & 1` while the next unit streams into the other one, so they never wait on global
+// memory except for experts with more than FAST_MAX_TOK assignments (later passes gather h directly).
+struct DecStageInfo {
+  FastExpert fe;
+  int tok[FAST_MAX_TOK];
+  float rw[FAST_MAX_TOK];
+  int a_begin, a_end;
+};
+
 __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
     const FastExpert* __restrict__ fast, const unsigned char* __restrict__ arena, const __half* __restrict__ h_gate,
     const __half* __restrict__ h_up, int h_rank, const int32_t* __restrict__ token_indices,
-    const int32_t* __restrict__ expert_offsets, const float* __restrict__ route_w, int rank_out, int T, int n_tiles,
-    int intermediate, int max_unit_bytes, int max_slots, float* __restrict__ rank_accum, int* __restrict__ status) {
+    const int32_t* __restrict__ expert_offsets, const float* __restrict__ route_w, int rank_out, int T, int num_experts,
+    int n_tiles, int intermediate, int max_unit_bytes, int max_slots, float* __restrict__ rank_accum,
+    int* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  const int e = blockIdx.x / n_tiles, tile = blockIdx.x - e * n_tiles;
-  const int a_begin = expert_offsets[e], a_end = expert_offsets[e + 1];
-  if (a_begin >= a_end) return;
-  __shared__ FastExpert fe;
-  if (threadIdx.x < sizeof(FastExpert) / 4)
-    reinterpret_cast<uint32_t*>(&fe)[threadIdx.x] = reinterpret_cast<const uint32_t*>(&fast[e])[threadIdx.x];
+  __shared__ DecStageInfo info[2];
+  __shared__ __align__(8) uint64_t bar_full[2][2];   // [stage][everything but down | down words]
+  __shared__ __align__(8) uint64_t bar_empty[2];
+  __shared__ int warp_cnt[9];
   const int slots_stride = dec_slots_stride(max_slots);
+  const size_t unit_bytes_al = align_up_c(static_cast<size_t>(max_unit_bytes), 128);
+  const size_t tabs_bytes_al = align_up_c(static_cast<size_t>(3) * (max_slots * 6 + 16), 128);
+  const size_t stage_bytes = dec_stage_bytes(max_unit_bytes, max_slots, h_rank);
   DecSmem sm;
+  int16_t* active;
   {
-    size_t o = 0;
+    size_t o = 2 * stage_bytes;
     sm.unit = smem_raw;
-    o += align_up_c(static_cast<size_t>(max_unit_bytes), 128);
+    sm.tabs = nullptr;
+    sm.tab_base = 0;
     sm.actp = reinterpret_cast<__half*>(smem_raw + o);
     o += static_cast<size_t>(2) * FAST_MAX_TOK * slots_stride * 2;
     sm.zp = reinterpret_cast<__half*>(smem_raw + o);
     o += static_cast<size_t>(FAST_MAX_TOK) * ZP_STRIDE * 2;
-    sm.corr = reinterpret_cast<float*>(smem_raw + o);
-    o += 3 * FAST_MAX_TOK * 4;
-    sm.tok = reinterpret_cast<int*>(smem_raw + o);
-    o += FAST_MAX_TOK * 4;
-    sm.rw = reinterpret_cast<float*>(smem_raw + o);
-    o += FAST_MAX_TOK * 4;
-    o = (o + 7) & ~static_cast<size_t>(7);
-    sm.bar = reinterpret_cast<uint64_t*>(smem_raw + o);
+    active = reinterpret_cast<int16_t*>(smem_raw + o);
+    sm.tok = nullptr;
+    sm.rw = nullptr;
   }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    mbar_init(&sm.bar[0], 1);
-    mbar_init(&sm.bar[1], 1);
+    mbar_init(&bar_full[0][0], 1);
+    mbar_init(&bar_full[0][1], 1);
+    mbar_init(&bar_full[1][0], 1);
+    mbar_init(&bar_full[1][1], 1);
+    mbar_init(&bar_empty[0], 8);
+    mbar_init(&bar_empty[1], 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned char* src = arena + fe.unit_base + static_cast<int64_t>(tile) * fe.unit_bytes;
-    const uint32_t bytes_a = static_cast<uint32_t>(fe.sec_off[5]);
-    const uint32_t bytes_b = static_cast<uint32_t>(fe.m[2].words) * 4u;
-    mbar_expect_tx(&sm.bar[0], bytes_a);
-    bulk_g2s(sm.unit, src, bytes_a, &sm.bar[0]);
-    mbar_expect_tx(&sm.bar[1], bytes_b);
-    bulk_g2s(sm.unit + bytes_a, src + bytes_a, bytes_b, &sm.bar[1]);
+  // ---- compact the active experts (ascending id), 288 candidates per round
+  int n_active = 0;
+  for (int base = 0; base < num_experts; base += DEC_THREADS) {
+    const int e = base + threadIdx.x;
+    const bool act = e < num_experts && expert_offsets[e + 1] > expert_offsets[e];
+    const unsigned m = __ballot_sync(0xffffffffu, act);
+    if (lane == 0) warp_cnt[warp] = __popc(m);
+    __syncthreads();
+    int before = n_active;
+    for (int w = 0; w < warp; ++w) before += warp_cnt[w];
+    if (act) active[before + __popc(m & ((1u << lane) - 1u))] = static_cast<int16_t>(e);
+    for (int w = 0; w < 9; ++w) n_active += warp_cnt[w];
+    __syncthreads();
   }
-  const int n_valid = min(N_TILE, intermediate - tile * N_TILE);
+  const int n_units = n_active * n_tiles;
+  if (static_cast<int>(blockIdx.x) >= n_units) return;
   bool ok = true;
-  bool first = true;
-  for (int a0 = a_begin; a0 < a_end; a0 += FAST_MAX_TOK) {
-    const int npass = min(FAST_MAX_TOK, a_end - a0);
-    if (threadIdx.x < FAST_MAX_TOK) {
-      const int n = threadIdx.x;
-      int tk = n < npass ? token_indices[a0 + n] : 0;
-      const bool good = n < npass && tk >= 0 && tk < T;
-      sm.tok[n] = good ? tk : 0;
-      sm.rw[n] = good ? route_w[a0 + n] : 0.f;
-    }
-    if (threadIdx.x < 3 * FAST_MAX_TOK) sm.corr[threadIdx.x] = 0.f;
-    __syncthreads();
-    if (first && !mbar_wait(&sm.bar[0], 0)) { ok = false; break; }
-    // ---- activation operand: actp[m][n][perm(slot)] = fp16(h[tok_n, rank(slot)] * s(slot) * scale(tile, slot))
-    {
-      const int pair = threadIdx.x >> 3, l8 = threadIdx.x & 7;
-      const int m = pair >> 4, n = pair & 15;
-      const int n_rows_used = ((npass + 7) >> 3) << 3;
-      if (n < n_rows_used) {
-        const FastMat& fm = fe.m[m];
-        const int16_t* rank_t = reinterpret_cast<const int16_t*>(arena + fm.tab_off);
-        const __half* s_t = reinterpret_cast<const __half*>(arena + fm.tab_off + fm.nslots * 2);
-        const __half* scale_t = reinterpret_cast<const __half*>(sm.unit + fe.sec_off[m]);
-        const __half* h = (m == 0 ? h_gate : h_up) + static_cast<int64_t>(sm.tok[n]) * h_rank;
-        __half* dst = sm.actp + (static_cast<size_t>(m) * FAST_MAX_TOK + n) * slots_stride;
-        const int b43 = fm.nblk[0] * 16, b3 = (fm.nblk[0] + fm.nblk[1]) * 16;
-        float csum = 0.f;
-        for (int slot = l8; slot < fm.nslots; slot += 8) {
-          float v = 0.f;
-          if (n < npass) {
-            const int rk = rank_t[slot];
-            if (rk >= 0 && rk < h_rank) v = __half2float(h[rk]) * __half2float(s_t[slot]) * __half2float(scale_t[slot]);
-          }
-          const __half hv = __float2half_rn(v);
-          dst[(slot & ~15) + kperm16(slot & 15)] = hv;
-          csum += (slot < b43 ? 8.f : (slot < b3 ? 4.f : 2.f)) * __half2float(hv);
-        }
-        csum += __shfl_xor_sync(0xffffffffu, csum, 1);
-        csum += __shfl_xor_sync(0xffffffffu, csum, 2);
-        csum += __shfl_xor_sync(0xffffffffu, csum, 4);
-        if (l8 == 0) sm.corr[m * FAST_MAX_TOK + n] = csum;
-      } else {
-        // keep the shuffles above convergent for the whole warp
-        float z = 0.f;
-        z += __shfl_xor_sync(0xffffffffu, z, 1);
-        z += __shfl_xor_sync(0xffffffffu, z, 2);
-        z += __shfl_xor_sync(0xffffffffu, z, 4);
+  long long bm_tick_ = clock64();
+  int* bm_timing_base = status + 8;
+  (void)bm_tick_; (void)bm_timing_base;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ producer warp
+    int it = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const int e = active[u / n_tiles], tile = u % n_tiles;
+      if (!mbar_wait(&bar_empty[buf], ((it >> 1) & 1) ^ 1)) { ok = false; break; }
+      DecStageInfo& si = info[buf];
+      for (int i = lane; i < static_cast<int>(sizeof(FastExpert) / 4); i += 32)
+        reinterpret_cast<uint32_t*>(&si.fe)[i] = reinterpret_cast<const uint32_t*>(&fast[e])[i];
+      const int a_begin = expert_offsets[e], a_end = expert_offsets[e + 1];
+      const int npass = min(FAST_MAX_TOK, a_end - a_begin);
+      int tk = 0;
+      if (lane < FAST_MAX_TOK) {
+        tk = lane < npass ? token_indices[a_begin + lane] : 0;
+        const bool good = lane < npass && tk >= 0 && tk < T;
+        tk = good ? tk : 0;
+        si.tok[lane] = tk;
+        si.rw[lane] = good ? route_w[a_begin + lane] : 0.f;
       }
+      if (lane == 0) { si.a_begin = a_begin; si.a_end = a_end; }
+      __syncwarp();
+      const FastExpert& fe = si.fe;
+      unsigned char* stage = smem_raw + buf * stage_bytes;
+      const unsigned char* src = arena + fe.unit_base + static_cast<int64_t>(tile) * fe.unit_bytes;
+      const uint32_t bytes_a = static_cast<uint32_t>(fe.sec_off[5]);
+      const uint32_t bytes_b = static_cast<uint32_t>(fe.m[2].words) * 4u;
+      const int tab0 = fe.m[0].tab_off;
+      const uint32_t tab_bytes = static_cast<uint32_t>(fe.m[2].tab_off + static_cast<int>(align_up_c(fe.m[2].nslots * 6, 16)) - tab0);
+      const uint32_t row_bytes = static_cast<uint32_t>(h_rank) * 2u;
+      if (lane == 0) {
+        mbar_expect_tx(&bar_full[buf][0], bytes_a + tab_bytes + 2u * npass * row_bytes);
+        bulk_g2s(stage, src, bytes_a, &bar_full[buf][0]);
+        bulk_g2s(stage + unit_bytes_al, arena + tab0, tab_bytes, &bar_full[buf][0]);
+        mbar_expect_tx(&bar_full[buf][1], bytes_b);
+        bulk_g2s(stage + bytes_a, src + bytes_a, bytes_b, &bar_full[buf][1]);
+      }
+      __syncwarp();
+      if (lane < 2 * npass) {
+        const int m = lane / npass, n = lane - m * npass;
+        const int tkn = __shfl_sync(__activemask(), tk, n);
+        const __half* hsrc = (m == 0 ? h_gate : h_up) + static_cast<int64_t>(tkn) * h_rank;
+        bulk_g2s(stage + unit_bytes_al + tabs_bytes_al + (static_cast<size_t>(m) * FAST_MAX_TOK + n) * row_bytes, hsrc, row_bytes,
+                 &bar_full[buf][0]);
+      }
+      __syncwarp();
     }
-    __syncthreads();
-    if (npass <= 8) decode_pass<1>(fe, sm, slots_stride, tile, n_valid, npass, rank_out, rank_accum, arena, first, &ok);
-    else decode_pass<2>(fe, sm, slots_stride, tile, n_valid, npass, rank_out, rank_accum, arena, first, &ok);
-    if (!ok) break;
-    first = false;
-    __syncthreads();
+    if (!ok && lane == 0) atomicExch(status, BM_ERR_TIMEOUT);
+    return;
   }
-  if (!ok) {
-    if (threadIdx.x == 0) atomicExch(status, BM_ERR_TIMEOUT);
-    // give copies still in flight a bounded chance to land before the CTA's shared memory is released
-    mbar_wait(&sm.bar[0], 0);
-    mbar_wait(&sm.bar[1], 0);
+
+  // -------------------------------------------------------------------- compute warps
+  int it = 0;
+  for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++it) {
+    const int buf = it & 1;
+    const uint32_t parity = (it >> 1) & 1;
+    const int tile = u % n_tiles;
+    const int n_valid = min(N_TILE, intermediate - tile * N_TILE);
+    unsigned char* stage = smem_raw + buf * stage_bytes;
+    if (!mbar_wait(&bar_full[buf][0], parity)) { ok = false; break; }
+    BM_TICK(0);
+    DecStageInfo& si = info[buf];
+    const FastExpert& fe = si.fe;
+    DecSmem cur = sm;
+    cur.unit = stage;
+    cur.tabs = stage + unit_bytes_al;
+    cur.tab_base = fe.m[0].tab_off;
+    cur.tok = si.tok;
+    cur.rw = si.rw;
+    const __half* hrows = reinterpret_cast<const __half*>(stage + unit_bytes_al + tabs_bytes_al);
+    const int a_begin = si.a_begin, a_end = si.a_end;
+    for (int a0 = a_begin; a0 < a_end && ok; a0 += FAST_MAX_TOK) {
+      const int npass = min(FAST_MAX_TOK, a_end - a0);
+      const bool staged = a0 == a_begin;
+      if (!staged) {
+        // later passes of a crowded expert: token ids and h rows come from global memory
+        consumer_sync();
+        if (threadIdx.x < FAST_MAX_TOK) {
+          const int n = threadIdx.x;
+          const int tk = n < npass ? token_indices[a0 + n] : 0;
+          const bool good = n < npass && tk >= 0 && tk < T;
+          si.tok[n] = good ? tk : 0;
+          si.rw[n] = good ? route_w[a0 + n] : 0.f;
+        }
+        consumer_sync();
+      }
+      // ---- activation operand: actp[m][n][perm(slot)] = fp16(h[tok_n, rank(slot)] * s(slot) * scale(tile, slot))
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        const int nslots = fe.m[m].nslots;
+        const int16_t* rank_t = reinterpret_cast<const int16_t*>(cur.tabs + (fe.m[m].tab_off - cur.tab_base));
+        const __half* s_t = reinterpret_cast<const __half*>(cur.tabs + (fe.m[m].tab_off - cur.tab_base) + nslots * 2);
+        const __half* scale_t = reinterpret_cast<const __half*>(stage + fe.sec_off[m]);
+        const __half* hg = m == 0 ? h_gate : h_up;
+        const __half* hs = hrows + static_cast<size_t>(m) * FAST_MAX_TOK * h_rank;
+        __half* dst = cur.actp + static_cast<size_t>(m) * FAST_MAX_TOK * slots_stride;
+        for (int slot = threadIdx.x; slot < nslots; slot += DEC_CONSUMERS) {
+          const int rk = rank_t[slot];
+          const float f = __half2float(s_t[slot]) * __half2float(scale_t[slot]);
+          const bool live = rk >= 0 && rk < h_rank;
+          const int pos = (slot & ~15) + kperm16(slot & 15);
+          float hv[FAST_MAX_TOK];
+#pragma unroll
+          for (int n = 0; n < FAST_MAX_TOK; ++n) {
+            hv[n] = 0.f;
+            if (live && n < npass)
+              hv[n] = __half2float(staged ? hs[n * h_rank + rk] : hg[static_cast<int64_t>(si.tok[n]) * h_rank + rk]);
+          }
+#pragma unroll
+          for (int n = 0; n < FAST_MAX_TOK; ++n) dst[n * slots_stride + pos] = __float2half_rn(hv[n] * f);
+        }
+      }
+      consumer_sync();
+      BM_TICK(1);
+      decode_pass<1>(fe, cur, slots_stride, tile, n_valid, npass, rank_out, rank_accum, arena, &bar_full[buf][1], parity, &ok,
+                     bm_tick_, bm_timing_base);
+      BM_TICK(6);
+    }
+    consumer_sync();
+    if (lane == 0) mbar_arrive(&bar_empty[buf]);
+    BM_TICK(7);
   }
+  if (!ok && threadIdx.x == 0) atomicExch(status, BM_ERR_TIMEOUT);
 }
 
 int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                           const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st) {
-  const size_t smem = dec_smem_bytes(L->max_unit_bytes, L->max_slots);
+  const size_t smem = dec_smem_bytes(L->max_unit_bytes, L->max_slots, L->rank_in);
   BM_REQUIRE(smem <= 220 * 1024, BM_ERR_UNSUPPORTED, "experts_decode: unit of %d bytes does not fit shared memory",
              L->max_unit_bytes);
+  BM_REQUIRE(L->num_experts <= DEC_MAX_E, BM_ERR_UNSUPPORTED, "experts_decode: more than %d experts", DEC_MAX_E);
+  BM_REQUIRE(L->rank_in % 8 == 0 && (reinterpret_cast<uintptr_t>(h_gate) & 15u) == 0 && (reinterpret_cast<uintptr_t>(h_up) & 15u) == 0,
+             BM_ERR_INVALID_ARG, "experts_decode: h_gate / h_up rows must be 16-byte aligned (rank %d)", L->rank_in);
   static int attr_set_for = -1;
+  static int sm_count = 148;
   if (attr_set_for != L->device) {
     BM_CUDA(cudaFuncSetAttribute(experts_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    BM_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, L->device));
     attr_set_for = L->device;
   }
-  experts_decode_kernel<<<L->num_experts * L->n_tiles, DEC_THREADS, smem, st>>>(
+  const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+  int grid = sm_count * per_sm;
+  const int max_units = L->num_experts * L->n_tiles;
+  if (grid > max_units) grid = max_units;
+  experts_decode_kernel<<<grid, DEC_THREADS, smem, st>>>(
       L->fast_dev, static_cast<const unsigned char*>(L->arena), h_gate, h_up, L->rank_in, token_indices, expert_offsets,
-      route_w, L->rank_out, T, L->n_tiles, L->intermediate, L->max_unit_bytes, L->max_slots, rank_accum, L->status_dev);
+      route_w, L->rank_out, T, L->num_experts, L->n_tiles, L->intermediate, L->max_unit_bytes, L->max_slots, rank_accum,
+      L->status_dev);
   BM_LAUNCH_CHECK("experts_decode_kernel");
   return BM_OK;
 }

@@ -20,6 +20,20 @@ int set_error(int status, const char* fmt, ...) {
 
 // from the other translation units
 int launch_gemm_nt(const GemmArgs& g, int problems, cudaStream_t st);
+struct SkinnyArgs {
+  const __half* W[2];
+  void* C[2];
+  const void* X;
+  const void* residual;
+  int rows_per_w, n_w;
+  int N, K;
+  int x_dtype, c_dtype;
+  int round_x_f16;
+  int splits;
+  int mrows;
+};
+int launch_skinny_nt(SkinnyArgs a, cudaStream_t st);
+constexpr int SKINNY_MAX_TOKENS = 256;
 void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P);
 int build_fast(bm_layer* L, const FastPlan& P, cudaStream_t st);
 size_t fast_build_scratch_bytes(const FastPlan& P);
@@ -346,6 +360,18 @@ extern "C" int bm_basis_project(const bm_layer_t* L, const void* x, int x_dtype,
   BM_REQUIRE(T >= 0 && x_dtype >= BM_F16 && x_dtype <= BM_F32, BM_ERR_INVALID_ARG, "basis_project: bad arguments");
   if (T == 0) return BM_OK;
   BM_REQUIRE(x && h_gate && h_up, BM_ERR_INVALID_ARG, "basis_project: null pointer");
+  if (T <= SKINNY_MAX_TOKENS && L->hidden % 128 == 0 && L->rank_in % 32 == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    SkinnyArgs a{};
+    a.W[0] = L->vh_gate; a.W[1] = L->vh_up;
+    a.C[0] = h_gate; a.C[1] = h_up;
+    a.X = x; a.residual = nullptr;
+    a.rows_per_w = L->rank_in; a.n_w = 2;
+    a.N = T; a.K = L->hidden;
+    a.x_dtype = x_dtype; a.c_dtype = BM_F16; a.round_x_f16 = 1;
+    a.splits = 8; a.mrows = 32;
+    return launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
+  }
   GemmArgs g{};
   g.A[0] = g.A[1] = x;
   g.B[0] = L->vh_gate;
@@ -399,6 +425,17 @@ extern "C" int bm_combine_down_basis(const bm_layer_t* L, const float* rank_accu
   BM_REQUIRE(T >= 0 && y_dtype >= BM_F16 && y_dtype <= BM_F32, BM_ERR_INVALID_ARG, "combine: bad arguments");
   if (T == 0) return BM_OK;
   BM_REQUIRE(rank_accum && y, BM_ERR_INVALID_ARG, "combine: null pointer");
+  if (T <= SKINNY_MAX_TOKENS && L->rank_out % 16 == 0 && L->hidden % 16 == 0 && L->rank_out <= 1024) {
+    SkinnyArgs a{};
+    a.W[0] = L->u_down; a.W[1] = L->u_down;
+    a.C[0] = y; a.C[1] = y;
+    a.X = rank_accum; a.residual = residual;
+    a.rows_per_w = L->hidden; a.n_w = 1;
+    a.N = T; a.K = L->rank_out;
+    a.x_dtype = BM_F32; a.c_dtype = y_dtype; a.round_x_f16 = 1;
+    a.splits = 1; a.mrows = 16;
+    return launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
+  }
   GemmArgs g{};
   g.A[0] = g.A[1] = rank_accum;
   g.B[0] = g.B[1] = L->u_down;
@@ -431,10 +468,9 @@ extern "C" int bm_layer_forward(const bm_layer_t* L, const void* x, int x_dtype,
   BM_REQUIRE(workspace && workspace_bytes >= w.total && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
              BM_ERR_WORKSPACE, "layer_forward: workspace must be 256-byte aligned and hold %zu bytes (%zu given)", w.total,
              workspace_bytes);
-  int rc = bm_route_topk(logits, logits_dtype, T, num_routed, k, renorm, weight_round, w.topk_idx, w.topk_w, stream);
-  if (rc) return rc;
-  rc = bm_route_build(w.topk_idx, w.topk_w, global_to_local, T, k, L->num_experts, TILE_ROWS, w.token_indices,
-                      w.expert_offsets, w.route_flat, w.tile_table, w.counts, w.route_ws, w.route_ws_bytes, stream);
+  int rc = bm_route(logits, logits_dtype, T, num_routed, k, renorm, weight_round, global_to_local, L->num_experts, TILE_ROWS,
+                    w.topk_idx, w.topk_w, w.token_indices, w.expert_offsets, w.route_flat, w.tile_table, w.counts, w.route_ws,
+                    w.route_ws_bytes, stream);
   if (rc) return rc;
   rc = bm_basis_project(L, x, x_dtype, T, reinterpret_cast<uint16_t*>(w.h_gate), reinterpret_cast<uint16_t*>(w.h_up), stream);
   if (rc) return rc;

@@ -17,14 +17,11 @@ constexpr int ROUTE_WARPS = ROUTE_BLOCK / 32;
 
 // ---------------------------------------------------------------- top-k
 // One warp per token; probabilities live in a warp-private shared row.
-__global__ void __launch_bounds__(256) route_topk_kernel(const void* __restrict__ logits, int dtype, int T, int E, int k,
-                                                        int renorm, int weight_round, int32_t* __restrict__ topk_idx,
-                                                        float* __restrict__ topk_w) {
-  extern __shared__ float sm_prob[];  // [warps][E]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= T) return;
-  float* p = sm_prob + warp * E;
+// Top-k of one token by one warp; `p` is a warp-private shared row of E floats.
+__device__ __forceinline__ void warp_topk_token(const void* __restrict__ logits, int dtype, int t, int E, int k, int renorm,
+                                                int weight_round, float* p, int32_t* __restrict__ idx_out,
+                                                float* __restrict__ w_out) {
+  const int lane = threadIdx.x & 31;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) {
     const float v = load_act(logits, dtype, static_cast<int64_t>(t) * E + e);
@@ -69,9 +66,21 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const void* __restrict_
     float w = renorm ? my_w / wsum : my_w;
     if (weight_round == BM_ROUND_F16) w = __half2float(__float2half_rn(w));
     else if (weight_round == BM_ROUND_BF16) w = __bfloat162float(__float2bfloat16_rn(w));
-    topk_idx[static_cast<int64_t>(t) * k + lane] = my_i;
-    topk_w[static_cast<int64_t>(t) * k + lane] = w;
+    idx_out[static_cast<int64_t>(t) * k + lane] = my_i;
+    w_out[static_cast<int64_t>(t) * k + lane] = w;
   }
+  __syncwarp();
+}
+
+// One warp per token; probabilities live in a warp-private shared row.
+__global__ void __launch_bounds__(256) route_topk_kernel(const void* __restrict__ logits, int dtype, int T, int E, int k,
+                                                        int renorm, int weight_round, int32_t* __restrict__ topk_idx,
+                                                        float* __restrict__ topk_w) {
+  extern __shared__ float sm_prob[];  // [warps][E]
+  const int warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  warp_topk_token(logits, dtype, t, E, k, renorm, weight_round, sm_prob + warp * E, topk_idx, topk_w);
 }
 
 // ---------------------------------------------------------------- permutation
@@ -107,9 +116,10 @@ __device__ __forceinline__ RouteSmem carve_route_smem(unsigned char* base, int E
   return s;
 }
 
-static size_t route_smem_bytes(int E) {
-  return sizeof(int) * E + sizeof(int) * (E + 1) + sizeof(uint16_t) * ROUTE_WARPS * E + align_up(ROUTE_WARPS * E, 16);
+__host__ __device__ inline size_t route_smem_bytes_dev(int E) {
+  return (sizeof(int) * E + sizeof(int) * (E + 1) + sizeof(uint16_t) * ROUTE_WARPS * E + static_cast<size_t>(ROUTE_WARPS) * E + 15) / 16 * 16;
 }
+static size_t route_smem_bytes(int E) { return route_smem_bytes_dev(E); }
 
 // Per-block counting shared by the fused and the multi-block paths.  Returns this
 // thread's rank inside its warp; warp_base / block_count are valid after the call.
@@ -213,6 +223,39 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) route_build_fused_kernel(
   }
   __syncthreads();
   // reuse block_count / warp_base storage as scratch for the tile table
+  write_tile_table(s.scan, E, tile_rows, tile_table, max_tiles, counts, reinterpret_cast<int*>(s.warp_base), s.block_count);
+}
+
+// T*k <= ROUTE_BLOCK: top-k of every token and the whole permutation in one block, one launch.
+__global__ void __launch_bounds__(ROUTE_BLOCK) route_all_fused_kernel(
+    const void* __restrict__ logits, int dtype, int T, int E_routed, int k, int renorm, int weight_round,
+    const int32_t* __restrict__ g2l, int E, int tile_rows, int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
+    int32_t* __restrict__ token_indices, int32_t* __restrict__ expert_offsets, float* __restrict__ route_flat,
+    int32_t* __restrict__ tile_table, int max_tiles, int32_t* __restrict__ counts) {
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  RouteSmem s = carve_route_smem(sm_raw, E);
+  float* prob = reinterpret_cast<float*>(sm_raw + route_smem_bytes_dev(E));   // [ROUTE_WARPS][E_routed]
+  const int warp = threadIdx.x >> 5;
+  for (int t = warp; t < T; t += ROUTE_WARPS)
+    warp_topk_token(logits, dtype, t, E_routed, k, renorm, weight_round, prob + warp * E_routed, topk_idx, topk_w);
+  __threadfence_block();
+  __syncthreads();
+  const int A = T * k;
+  const int i = threadIdx.x;
+  int e = -1;
+  if (i < A) {
+    e = topk_idx[i];
+    if (g2l) e = g2l[e];
+  }
+  const int rank_w = block_count_and_rank(e, E, s);
+  block_exclusive_scan(s.block_count, s.scan, E);
+  for (int x = threadIdx.x; x <= E; x += blockDim.x) expert_offsets[x] = s.scan[x];
+  if (e >= 0) {
+    const int pos = s.scan[e] + s.warp_base[(threadIdx.x >> 5) * E + e] + rank_w;
+    token_indices[pos] = i / k;
+    route_flat[pos] = topk_w[i];
+  }
+  __syncthreads();
   write_tile_table(s.scan, E, tile_rows, tile_table, max_tiles, counts, reinterpret_cast<int*>(s.warp_base), s.block_count);
 }
 
@@ -355,4 +398,34 @@ extern "C" int bm_route_build(const int32_t* topk_idx, const float* topk_w, cons
                                                            expert_offsets, token_indices, route_flat);
   BM_LAUNCH_CHECK("route_scatter_kernel");
   return BM_OK;
+}
+
+extern "C" int bm_route(const void* logits, int logits_dtype, int32_t T, int32_t E_routed, int32_t k, int32_t renorm,
+                        int32_t weight_round, const int32_t* global_to_local, int32_t num_local, int32_t tile_rows,
+                        int32_t* topk_idx, float* topk_w, int32_t* token_indices, int32_t* expert_offsets,
+                        float* route_flat, int32_t* tile_table, int32_t* counts, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+  using namespace bm;
+  const int64_t A = static_cast<int64_t>(T) * k;
+  const size_t fused_smem = route_smem_bytes(num_local > 0 ? num_local : 1) + sizeof(float) * ROUTE_WARPS * (E_routed > 0 ? E_routed : 1);
+  if (T > 0 && A <= ROUTE_BLOCK && E_routed > 0 && E_routed <= ROUTE_MAX_E && num_local > 0 && num_local <= ROUTE_MAX_E &&
+      k > 0 && k <= 32 && k <= E_routed && tile_rows > 0 && fused_smem <= 200 * 1024) {
+    BM_REQUIRE(logits && topk_idx && topk_w && token_indices && expert_offsets && route_flat, BM_ERR_INVALID_ARG,
+               "route: null pointer");
+    BM_REQUIRE(logits_dtype >= BM_F16 && logits_dtype <= BM_F32, BM_ERR_INVALID_ARG, "route: bad logits dtype");
+    static bool attr_done = false;
+    if (!attr_done) {
+      BM_CUDA(cudaFuncSetAttribute(route_all_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      attr_done = true;
+    }
+    route_all_fused_kernel<<<1, ROUTE_BLOCK, fused_smem, static_cast<cudaStream_t>(stream)>>>(
+        logits, logits_dtype, T, E_routed, k, renorm, weight_round, global_to_local, num_local, tile_rows, topk_idx, topk_w,
+        token_indices, expert_offsets, route_flat, tile_table, bm_route_max_tiles(T, k, num_local, tile_rows), counts);
+    BM_LAUNCH_CHECK("route_all_fused_kernel");
+    return BM_OK;
+  }
+  int rc = bm_route_topk(logits, logits_dtype, T, E_routed, k, renorm, weight_round, topk_idx, topk_w, stream);
+  if (rc) return rc;
+  return bm_route_build(topk_idx, topk_w, global_to_local, T, k, num_local, tile_rows, token_indices, expert_offsets,
+                        route_flat, tile_table, counts, workspace, workspace_bytes, stream);
 }

@@ -1,0 +1,180 @@
+// Shared-basis products for small token counts:  C[n][m] = sum_k W[m][k] * X[n][k]
+//   h_gate / h_up = x . Vh^T        (W = Vh_gate | Vh_up, K = hidden, split over a cluster)
+//   y = fp16(rank_accum) . U_down^T  (W = U_down, K = rank_out) (+ residual)
+// These are weight-streaming GEMVs: every CTA reads a [rows x k-slice] block of W exactly once,
+// keeps it in shared memory and multiplies it with the (few) token rows on the tensor cores
+// (mma.sync m16n8k16, W rows as the A operand, tokens as N).  When the contraction is long
+// (hidden = 2048) it is split over the CTAs of a thread-block cluster, whose partial sums are
+// reduced through distributed shared memory, so no atomics and no second pass are needed.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace bm {
+
+constexpr int SK_THREADS = 256;
+constexpr int SK_NTOK = 64;   // tokens per chunk
+
+struct SkinnyArgs {
+  const __half* W[2];    // up to two weight matrices stacked along m (rows_per_w rows each)
+  void* C[2];            // C[i] is [N, rows_per_w]
+  const void* X;         // [N, K]
+  const void* residual;  // [N, rows_per_w] or null (W[0] only)
+  int rows_per_w, n_w;   // total m = rows_per_w * n_w
+  int N, K;
+  int x_dtype, c_dtype;
+  int round_x_f16;       // X is fp32 and is rounded through fp16 (always true for fp32 here)
+  int splits;            // cluster size along k
+  int mrows;             // W rows per CTA: 16 or 32
+};
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// smem: Ws [mrows][ks + 8] half | Xs [64][ks + 8] half | part [mrows][64 + 1] float (only when splits > 1)
+__global__ void __launch_bounds__(SK_THREADS) skinny_nt_kernel(SkinnyArgs a) {
+  extern __shared__ __align__(16) unsigned char sk_smem[];
+  const int ks = a.K / a.splits;
+  const int stride = ks + 8;
+  __half* Ws = reinterpret_cast<__half*>(sk_smem);
+  __half* Xs = Ws + static_cast<size_t>(a.mrows) * stride;
+  float* part = reinterpret_cast<float*>(Xs + static_cast<size_t>(SK_NTOK) * stride);
+  const int split = blockIdx.x % a.splits;
+  const int m0 = (blockIdx.x / a.splits) * a.mrows;     // first global output row of this CTA
+  const int wsel = m0 / a.rows_per_w;                    // which stacked matrix
+  const int mloc0 = m0 - wsel * a.rows_per_w;
+  const __half* W = a.W[wsel] + static_cast<size_t>(mloc0) * a.K + static_cast<size_t>(split) * ks;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+  // W slice -> smem, 16-byte vectors
+  const int vec_per_row = ks / 8;
+  for (int v = threadIdx.x; v < a.mrows * vec_per_row; v += SK_THREADS) {
+    const int r = v / vec_per_row, c = (v - r * vec_per_row) * 8;
+    const uint4 val = *reinterpret_cast<const uint4*>(W + static_cast<size_t>(r) * a.K + c);
+    *reinterpret_cast<uint4*>(Ws + static_cast<size_t>(r) * stride + c) = val;
+  }
+  const int mblocks = a.mrows / 16;
+  for (int n0 = 0; n0 < a.N; n0 += SK_NTOK) {
+    const int nn = min(SK_NTOK, a.N - n0);
+    const int nblocks = (nn + 7) / 8;
+    __syncthreads();   // previous chunk's readers of Xs / part are done
+    // X slice -> fp16 smem
+    for (int v = threadIdx.x; v < nblocks * 8 * vec_per_row; v += SK_THREADS) {
+      const int r = v / vec_per_row, c = (v - r * vec_per_row) * 8;
+      __half out[8];
+      if (r < nn) {
+        const size_t idx = static_cast<size_t>(n0 + r) * a.K + static_cast<size_t>(split) * ks + c;
+        if (a.x_dtype == BM_F16) {
+          *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(a.X) + idx);
+        } else if (a.x_dtype == BM_BF16) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.X) + idx);
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            out[2 * i] = __float2half_rn(__uint_as_float(w[i] << 16));
+            out[2 * i + 1] = __float2half_rn(__uint_as_float(w[i] & 0xffff0000u));
+          }
+        } else {
+          const float4 f0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.X) + idx);
+          const float4 f1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.X) + idx + 4);
+          out[0] = __float2half_rn(f0.x); out[1] = __float2half_rn(f0.y); out[2] = __float2half_rn(f0.z); out[3] = __float2half_rn(f0.w);
+          out[4] = __float2half_rn(f1.x); out[5] = __float2half_rn(f1.y); out[6] = __float2half_rn(f1.z); out[7] = __float2half_rn(f1.w);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] = __float2half(0.f);
+      }
+      *reinterpret_cast<uint4*>(Xs + static_cast<size_t>(r) * stride + c) = *reinterpret_cast<uint4*>(out);
+    }
+    __syncthreads();
+    // (mblock, nblock) items round-robin over the warps
+    for (int item = warp; item < mblocks * nblocks; item += SK_THREADS / 32) {
+      const int mb = item % mblocks, nb = item / mblocks;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const __half* wa = Ws + static_cast<size_t>(mb * 16 + g) * stride + 2 * t;
+      const __half* xb = Xs + static_cast<size_t>(nb * 8 + g) * stride + 2 * t;
+#pragma unroll 4
+      for (int k = 0; k < ks; k += 16) {
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(wa + k);
+        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(wa + k + 8 * stride);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(wa + k + 8);
+        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(wa + k + 8 * stride + 8);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xb + k);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xb + k + 8);
+        mma16816(acc, a0, a1, a2, a3, b0, b1);
+      }
+      // D: rows m = mb*16 + g (+8), cols n = nb*8 + 2t (+1)
+      if (a.splits == 1) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int m = mloc0 + mb * 16 + g + (j >= 2 ? 8 : 0), n = nb * 8 + 2 * t + (j & 1);
+          if (n < nn) {
+            const size_t idx = static_cast<size_t>(n0 + n) * a.rows_per_w + m;
+            float v = acc[j];
+            if (a.residual && wsel == 0) v += load_act(a.residual, a.c_dtype, idx);
+            store_act(a.C[wsel], a.c_dtype, idx, v);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          part[(mb * 16 + g + (j >= 2 ? 8 : 0)) * (SK_NTOK + 1) + nb * 8 + 2 * t + (j & 1)] = acc[j];
+      }
+    }
+    if (a.splits > 1) {
+      cg::cluster_group cluster = cg::this_cluster();
+      cluster.sync();   // every CTA's partial tile is complete
+      // CTA `split` reduces outputs o = split, split + splits, ... of the mrows x nn tile
+      const int total = a.mrows * nblocks * 8;
+      for (int o = split + a.splits * threadIdx.x; o < total; o += a.splits * SK_THREADS) {
+        const int m = o % a.mrows, n = o / a.mrows;
+        float v = 0.f;
+        for (int r = 0; r < a.splits; ++r) {
+          const float* remote = cluster.map_shared_rank(part, r);
+          v += remote[m * (SK_NTOK + 1) + n];
+        }
+        if (n < nn) {
+          const size_t idx = static_cast<size_t>(n0 + n) * a.rows_per_w + mloc0 + m;
+          if (a.residual && wsel == 0) v += load_act(a.residual, a.c_dtype, idx);
+          store_act(a.C[wsel], a.c_dtype, idx, v);
+        }
+      }
+      cluster.sync();   // nobody overwrites `part` or exits while it is being read remotely
+    }
+  }
+}
+
+// Returns BM_ERR_UNSUPPORTED when the shape does not fit; the caller then uses the general GEMM.
+int launch_skinny_nt(SkinnyArgs a, cudaStream_t st) {
+  BM_REQUIRE(a.K % (16 * a.splits) == 0 && a.rows_per_w % a.mrows == 0, BM_ERR_UNSUPPORTED, "skinny_nt: shape does not tile");
+  const int ks = a.K / a.splits;
+  size_t smem = static_cast<size_t>(a.mrows + SK_NTOK) * (ks + 8) * 2;
+  if (a.splits > 1) smem += static_cast<size_t>(a.mrows) * (SK_NTOK + 1) * 4;
+  BM_REQUIRE(smem <= 160 * 1024, BM_ERR_UNSUPPORTED, "skinny_nt: k-slice of %d does not fit shared memory", ks);
+  static bool attr_done = false;
+  if (!attr_done) {
+    BM_CUDA(cudaFuncSetAttribute(skinny_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    attr_done = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.rows_per_w * a.n_w / a.mrows) * a.splits);
+  cfg.blockDim = dim3(SK_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = a.splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  BM_CUDA(cudaLaunchKernelEx(&cfg, skinny_nt_kernel, a));
+  return BM_OK;
+}
+
+}  // namespace bm
