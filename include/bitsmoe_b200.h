@@ -133,6 +133,23 @@ BM_API int bm_route_build(const int32_t* topk_idx, const float* topk_w, const in
                    int32_t* token_indices, int32_t* expert_offsets, float* route_flat,
                    int32_t* tile_table, int32_t* counts, void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  Same result as bm_route_build, for hosts that cannot give the
+ * library scratch memory (code that must stay off the CUDA allocator while serving, or a plug-in that
+ * only ever receives input and output pointers): the per-block histogram table lives in a fixed
+ * 1 MiB array inside the library instead of a caller workspace.  Calls nothing that allocates.
+ *  - limit: ceil(T*k/1024) * num_local * 4 bytes must fit bm_route_build_static_capacity();
+ *    larger problems return BM_ERR_WORKSPACE and should use bm_route_build;
+ *  - the first call on each device looks up the array's device address (that device must be
+ *    current); make that first call before starting any stream capture;
+ *  - all calls on a device share the one array: it still holds the previous call's table on
+ *    entry (every entry used is rewritten before it is read, nothing needs to be zero), and two
+ *    calls whose kernels overlap on the GPU (different streams) race on it. */
+BM_API size_t bm_route_build_static_capacity(void);
+BM_API int bm_route_build_static(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local,
+                                 int32_t T, int32_t k, int32_t num_local, int32_t tile_rows,
+                                 int32_t* token_indices, int32_t* expert_offsets, float* route_flat,
+                                 int32_t* tile_table, int32_t* counts, void* stream);
+
 /* Router tail and routing build in one call (a single launch when T*k <= 1024): the sequence
  * bitsmoe/models/qwen3moe/bitsmoe_block.py:47-51 -> bitsmoe/models/base_block.py:258-289. */
 BM_API int bm_route(const void* logits, int logits_dtype, int32_t T, int32_t E_routed, int32_t k, int32_t renorm,
