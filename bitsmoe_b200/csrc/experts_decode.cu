@@ -12,6 +12,7 @@
 // expert split the contraction of the down product; their partial sums meet in rank_accum through
 // fp32 atomics (as in bitsmoe/algorithms/cpp/mlp_forward.cu:2036-2066).
 #include "fast_layout.cuh"
+#include "tc05.cuh"
 
 namespace bm {
 
@@ -46,20 +47,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                "l"(src), "r"(bytes), "r"(smem_addr(bar))
                : "memory");
 }
-// Bounded wait: false if the phase did not complete within the spin limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_addr(bar);
-  for (uint32_t i = 0; i < DEC_SPIN_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return tc::mbar_wait(bar, parity); }
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"

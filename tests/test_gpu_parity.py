@@ -264,3 +264,21 @@ def test_decode_path_refused_without_arena(mixed):
     args = [o[k].to(DEV) for k in ("h_gate", "h_up", "token_indices", "expert_offsets", "route_flat")]
     with pytest.raises(capi.BitsMoEError, match="decode path needs"):
         packed.experts_forward(*args, path=capi.PATH_DECODE)
+
+
+@pytest.mark.parametrize("T", [300, 1000])
+def test_tensor_core_basis_products_vs_oracle(q30_small, T):
+    """x.Vh^T and rank_accum.U_down^T for prefill-sized batches run on tcgen05 (TMEM accumulators)."""
+    layer, packed, _ = q30_small
+    cfg = layer.cfg
+    x = synth.activations(cfg, T, seed=15)
+    hg, hu = packed.basis_project(x.to(DEV))
+    packed.check_status()
+    helpers.assert_close(hg, oforward.basis_project(x, layer.vh_gate.cpu()), rtol=2e-3, atol=2e-3, what="h_gate (tcgen05)")
+    helpers.assert_close(hu, oforward.basis_project(x, layer.vh_up.cpu()), rtol=2e-3, atol=2e-3, what="h_up (tcgen05)")
+    acc = torch.randn(T, cfg.rank) * 0.05
+    res = torch.randn(T, cfg.hidden).to(torch.bfloat16)
+    y = packed.combine_down_basis(acc.to(DEV), torch.bfloat16, residual=res.to(DEV))
+    packed.check_status()
+    want = oforward.down_basis(acc, layer.u_down.cpu(), torch.float32) + res.float()
+    helpers.assert_close(y, want, rtol=1e-2, atol=1e-2, what="down basis + residual (tcgen05)")
