@@ -45,6 +45,7 @@ void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P) {
       fm.tab_off = static_cast<int32_t>(off);
       off += align_up(static_cast<size_t>(fm.nslots) * 6, 16);
       if (fm.nslots > P->max_slots) P->max_slots = fm.nslots;
+      if (fm.words > P->max_words) P->max_words = fm.words;
       if (off > (1ull << 31)) return;
     }
   }
@@ -127,7 +128,8 @@ __global__ void __launch_bounds__(128) repack_tables_kernel(const ExpertDev* __r
         break;
       }
     }
-    scale_out[slot] = sc;
+    // gate / up scales are stored in the contraction order of the MMA operands (pairs (s, s+8) adjacent)
+    scale_out[w < 2 ? (slot & ~15) + kperm16(slot & 15) : slot] = sc;
     if (tile == 0) {
       int rk = row >= 0 ? md.rank_idx[row] : -1;
       if (rk < 0 || rk > 32000) rk = -1;

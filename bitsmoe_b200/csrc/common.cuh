@@ -98,7 +98,7 @@ struct FastPlan {
   size_t tabs_off = 0;                // per-matrix rank/s/row tables
   size_t units_off = 0;
   size_t total = 0;
-  int max_unit_bytes = 0, max_slots = 0;
+  int max_unit_bytes = 0, max_slots = 0, max_words = 0;
   int* status_dev = nullptr;       // device flag set by a kernel whose bounded wait gave up
 };
 
@@ -154,6 +154,6 @@ struct bm_layer {
   bool fast_ok = false;            // every slab is 2/3/4-bit and shapes fit the decode / tensor paths
   const bm::FastExpert* fast_dev = nullptr;   // in the arena
   std::vector<bm::FastExpert> fast_host;
-  int max_unit_bytes = 0, max_slots = 0;
+  int max_unit_bytes = 0, max_slots = 0, max_words = 0;
   int* status_dev = nullptr;       // device flag set by a kernel whose bounded wait gave up
 };

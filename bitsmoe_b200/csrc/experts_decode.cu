@@ -397,9 +397,9 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
         __half* dst = cur.actp + static_cast<size_t>(m) * FAST_MAX_TOK * slots_stride;
         for (int slot = threadIdx.x; slot < nslots; slot += DEC_CONSUMERS) {
           const int rk = rank_t[slot];
-          const float f = __half2float(s_t[slot]) * __half2float(scale_t[slot]);
-          const bool live = rk >= 0 && rk < h_rank;
           const int pos = (slot & ~15) + kperm16(slot & 15);
+          const float f = __half2float(s_t[slot]) * __half2float(scale_t[pos]);
+          const bool live = rk >= 0 && rk < h_rank;
           float hv[FAST_MAX_TOK];
 #pragma unroll
           for (int n = 0; n < FAST_MAX_TOK; ++n) {

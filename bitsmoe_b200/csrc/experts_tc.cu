@@ -1,0 +1,466 @@
+// Packed routed-expert forward for large token counts (prefill): fused mixed-bit grouped GEMM on the
+// 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
+//
+// Work item = (expert, block of up to 64 of its assignments).  One persistent CTA per SM walks the items.
+// For an item the three products of every 128-column tile run with the WEIGHTS as the 128-row operand:
+//   gate/up:  D_g[c, n] = sum_slot  W_g[c, slot] * act_g[n, slot]      (M = 128 columns c, N = 64 tokens)
+//   down:     D_d[slot, n] += sum_c W_d[slot, c] * z[n, c]             (M = 128 row slots x 3, N = 64 tokens)
+// so decode-like small N and prefill share one tile shape, and D_d accumulates over all tiles in TMEM.
+// Warp roles (448 threads):
+//   warps 0-3   epilogue: tcgen05.ld D_g/D_u -> z = silu(g)*u -> fp16 Z tile in shared memory; at the end of
+//               the item D_d -> * s * route weight -> fp32 atomics into rank_accum
+//   warp  4     producer: item descriptor, cp.async.bulk of the packed words + scales of (tile, matrix)
+//               sections into a 3-slot ring
+//   warp  5     MMA issue (one thread) and tcgen05.commit to the ring / phase mbarriers
+//   warps 6-13  dequantisers: bit-plane words -> fp16 (q * scale) A-operand stages of 128 rows x 16 K in the
+//               canonical K-major core-matrix layout, 8-stage ring; they also build the activation operand
+//               act[n, slot] = fp16(h[token, rank(slot)] * s(slot)) once per item
+// Every mbarrier wait is bounded in time and aborts the whole CTA through a shared flag.
+#include "fast_layout.cuh"
+#include "tc05.cuh"
+
+namespace bm {
+
+constexpr int XT_NT = 64;                 // tokens (assignments) per item = MMA N
+constexpr int XT_THREADS = 448;
+constexpr int XT_EPI_WARPS = 4, XT_PRODUCER_WARP = 4, XT_MMA_WARP = 5, XT_DQ_WARP0 = 6, XT_DQ_WARPS = 8;
+constexpr int XT_RING = 8;                // A-operand stages
+constexpr int XT_STAGE_BYTES = 128 * 16 * 2;
+constexpr int XT_MAX_E = 1024;
+
+struct XtBars {
+  uint64_t sec_full[3], sec_empty[3];
+  uint64_t w_full[XT_RING], w_empty[XT_RING];
+  uint64_t act_ready, gu_done, z_ready, tmem_gu_free, down_done;
+};
+
+struct XtItem {
+  FastExpert fe;
+  int tok[XT_NT];
+  float rw[XT_NT];
+  int n, expert;
+};
+
+__device__ __forceinline__ bool xt_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t addr = tc::smem_u32(bar);
+  uint64_t t0 = 0;
+  for (uint32_t i = 0;; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity), "r"(20000u)
+        : "memory");
+    if (done) return true;
+    if (*abort_flag) return false;
+    if ((i & 15u) == 15u) {
+      const uint64_t now = tc::global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > tc::WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+    }
+  }
+}
+
+// 32 codes of a row pair (rows g and g+8 of a 16-row block, 16 contraction positions) -> fp16 values
+// (u - offset) * scale, as four 16-byte chunks: row g positions 0-7 / 8-15, row g+8 positions 0-7 / 8-15 of the
+// block in the order k = (0,8,1,9,2,10,3,11 | 4,12,5,13,6,14,7,15).  `sc_lo[s]` = scale pair applied to the
+// register holding positions (s, s+8) of row g, `sc_hi[s]` the same for row g+8.
+template <int BITS>
+__device__ __forceinline__ void dequant_rowpair(const uint32_t* __restrict__ w, const __half2* sc_lo, const __half2* sc_hi,
+                                                uint4& g_c0, uint4& g_c1, uint4& h_c0, uint4& h_c1) {
+  uint32_t words[BITS];
+#pragma unroll
+  for (int p = 0; p < BITS; ++p) words[p] = w[p];
+  const uint32_t bias_bits = 0x64006400u + (1u << (BITS - 1)) * 0x00010001u;   // fp16x2 of 1024 + offset
+  const __half2 bias = *reinterpret_cast<const __half2*>(&bias_bits);
+  uint32_t lo[8], hi[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    uint32_t y = 0;
+#pragma unroll
+    for (int p = 0; p < BITS; ++p) y |= __funnelshift_r(words[p], words[p], (s - p) & 31) & (0x01010101u << p);
+    const uint32_t a = __byte_perm(y, 0x64646464u, 0x4140);   // (1024 + u) for row g,   positions s, s+8
+    const uint32_t b = __byte_perm(y, 0x64646464u, 0x4342);   // (1024 + u) for row g+8, positions s, s+8
+    __half2 va = __hsub2(*reinterpret_cast<const __half2*>(&a), bias);
+    __half2 vb = __hsub2(*reinterpret_cast<const __half2*>(&b), bias);
+    va = __hmul2(va, sc_lo[s]);
+    vb = __hmul2(vb, sc_hi[s]);
+    lo[s] = *reinterpret_cast<uint32_t*>(&va);
+    hi[s] = *reinterpret_cast<uint32_t*>(&vb);
+  }
+  g_c0 = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  g_c1 = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+  h_c0 = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  h_c1 = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+}
+
+// Writes one row-pair unit (mblock x, row g) of an A-operand stage: rows 16x+g and 16x+g+8, two K chunks.
+__device__ __forceinline__ void store_unit(unsigned char* stage, int x, int g, const uint4& g_c0, const uint4& g_c1,
+                                           const uint4& h_c0, const uint4& h_c1) {
+  unsigned char* p = stage + (2 * x) * 128 + g * 16;
+  *reinterpret_cast<uint4*>(p) = g_c0;
+  *reinterpret_cast<uint4*>(p + 2048) = g_c1;
+  *reinterpret_cast<uint4*>(p + 128) = h_c0;
+  *reinterpret_cast<uint4*>(p + 128 + 2048) = h_c1;
+}
+struct XtSmem {
+  unsigned char* act;     // [2][nchunks][XT_NT rows] canonical K-major, 16-byte chunks
+  unsigned char* z;       // [16 chunks][XT_NT rows]
+  unsigned char* ring;    // [XT_RING][XT_STAGE_BYTES]
+  unsigned char* sec[3];  // section buffers: [scale (sec_scale_bytes) | words]
+  int* prefix;            // [E + 1] items before each expert
+};
+
+__host__ __device__ inline size_t xt_sec_bytes(int max_slots, int max_words) {
+  return align_up_c(static_cast<size_t>(max_slots) * 2, 128) + align_up_c(static_cast<size_t>(max_words) * 4, 128);
+}
+__host__ __device__ inline size_t xt_smem_bytes(int max_slots, int max_words, int num_experts) {
+  size_t o = 0;
+  o += static_cast<size_t>(2) * XT_NT * max_slots * 2;      // act
+  o += static_cast<size_t>(XT_NT) * N_TILE * 2;             // z
+  o += static_cast<size_t>(XT_RING) * XT_STAGE_BYTES;       // ring
+  o += 3 * xt_sec_bytes(max_slots, max_words);
+  o += align_up_c(static_cast<size_t>(num_experts + 1) * 4, 128);
+  return o + 1024;                                          // slack for the 1024-byte base alignment
+}
+
+__global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
+    const FastExpert* __restrict__ fast, const unsigned char* __restrict__ arena, const __half* __restrict__ h_gate,
+    const __half* __restrict__ h_up, int h_rank, const int32_t* __restrict__ token_indices,
+    const int32_t* __restrict__ expert_offsets, const float* __restrict__ route_w, int rank_out, int T, int num_experts,
+    int n_tiles, int max_slots, int max_words, float* __restrict__ rank_accum, int* __restrict__ status) {
+  extern __shared__ unsigned char xt_raw[];
+  __shared__ __align__(8) XtBars bars;
+  __shared__ XtItem item;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  XtSmem sm;
+  {
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(xt_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    size_t o = 0;
+    sm.act = base; o += static_cast<size_t>(2) * XT_NT * max_slots * 2;
+    sm.z = base + o; o += static_cast<size_t>(XT_NT) * N_TILE * 2;
+    sm.ring = base + o; o += static_cast<size_t>(XT_RING) * XT_STAGE_BYTES;
+    for (int i = 0; i < 3; ++i) { sm.sec[i] = base + o; o += xt_sec_bytes(max_slots, max_words); }
+    sm.prefix = reinterpret_cast<int*>(base + o);
+  }
+  const size_t sec_scale_bytes = align_up_c(static_cast<size_t>(max_slots) * 2, 128);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 3; ++i) { tc::mbar_init(&bars.sec_full[i], 1); tc::mbar_init(&bars.sec_empty[i], XT_DQ_WARPS); }
+    for (int i = 0; i < XT_RING; ++i) { tc::mbar_init(&bars.w_full[i], 2); tc::mbar_init(&bars.w_empty[i], 1); }
+    tc::mbar_init(&bars.act_ready, 1);
+    tc::mbar_init(&bars.gu_done, 1);
+    tc::mbar_init(&bars.z_ready, XT_EPI_WARPS);
+    tc::mbar_init(&bars.tmem_gu_free, XT_EPI_WARPS);
+    tc::mbar_init(&bars.down_done, 1);
+    tc::mbar_init_fence();
+    abort_flag_s = 0;
+  }
+  if (warp == 0) tc::tmem_alloc(&tmem_slot, 512);
+  // items before each expert (an item = up to XT_NT consecutive assignments of one expert)
+  if (threadIdx.x == 32) {
+    int run = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      sm.prefix[e] = run;
+      run += (expert_offsets[e + 1] - expert_offsets[e] + XT_NT - 1) / XT_NT;
+    }
+    sm.prefix[num_experts] = run;
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  const int n_items = sm.prefix[num_experts];
+  const uint32_t idesc = tc::idesc_f16(128, XT_NT);
+  const uint32_t d_gate = tmem_base, d_up = tmem_base + XT_NT, d_down = tmem_base + 2 * XT_NT;
+
+  // running counters shared by construction between roles (every role advances them identically)
+  uint32_t ring_i = 0;      // A-operand stages produced / consumed so far
+  uint32_t gu_round = 0;    // gate/up rounds (one per tile) so far
+  uint32_t sec_round = 0;   // tiles so far (each uses the three section slots once)
+  uint32_t item_round = 0;
+
+  for (int it = blockIdx.x; it < n_items; it += gridDim.x, ++item_round) {
+    __syncthreads();   // previous item completely finished (TMEM read out, item info free)
+    if (warp == XT_PRODUCER_WARP) {
+      // locate the item: last expert e with prefix[e] <= it
+      int lo = 0, hi = num_experts - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (sm.prefix[mid] <= it) lo = mid; else hi = mid - 1;
+      }
+      const int e = lo;
+      const int a0 = expert_offsets[e] + (it - sm.prefix[e]) * XT_NT;
+      const int n = min(XT_NT, expert_offsets[e + 1] - a0);
+      for (int i = lane; i < static_cast<int>(sizeof(FastExpert) / 4); i += 32)
+        reinterpret_cast<uint32_t*>(&item.fe)[i] = reinterpret_cast<const uint32_t*>(&fast[e])[i];
+      for (int i = lane; i < XT_NT; i += 32) {
+        int tk = i < n ? token_indices[a0 + i] : 0;
+        const bool good = i < n && tk >= 0 && tk < T;
+        item.tok[i] = good ? tk : 0;
+        item.rw[i] = good ? route_w[a0 + i] : 0.f;
+      }
+      if (lane == 0) { item.n = n; item.expert = e; }
+    }
+    __syncthreads();
+    const FastExpert& fe = item.fe;
+    const int n_tok = item.n;
+    const int nblk_d = fe.m[2].nslots >> 4;
+    const int n_mt = (nblk_d + 7) >> 3;   // 128-row tiles of the down product (<= 3)
+
+    if (warp == XT_PRODUCER_WARP) {
+      // ------------------------------------------------------------------ producer
+      if (lane == 0) {
+        uint32_t sr = sec_round;
+        for (int tile = 0; tile < n_tiles && !*abort_flag; ++tile, ++sr) {
+          const unsigned char* unit = arena + fe.unit_base + static_cast<int64_t>(tile) * fe.unit_bytes;
+          for (int m = 0; m < 3; ++m) {
+            if (!xt_wait(&bars.sec_empty[m], (sr & 1) ^ 1, abort_flag)) break;
+            const uint32_t sb = static_cast<uint32_t>(fe.m[m].nslots) * 2u, wb = static_cast<uint32_t>(fe.m[m].words) * 4u;
+            tc::mbar_expect_tx(&bars.sec_full[m], sb + wb);
+            tc::bulk_g2s(sm.sec[m], unit + fe.sec_off[m], sb, &bars.sec_full[m]);
+            tc::bulk_g2s(sm.sec[m] + sec_scale_bytes, unit + fe.sec_off[3 + m], wb, &bars.sec_full[m]);
+          }
+        }
+      }
+    } else if (warp == XT_MMA_WARP) {
+      // ------------------------------------------------------------------ MMA issue
+      if (lane == 0) {
+        bool ok = xt_wait(&bars.act_ready, item_round & 1, abort_flag);
+        uint32_t ri = ring_i, gr = gu_round;
+        const uint32_t act_base = tc::smem_u32(sm.act), z_base = tc::smem_u32(sm.z), ring_base = tc::smem_u32(sm.ring);
+        const uint32_t act_m_bytes = static_cast<uint32_t>(XT_NT) * max_slots * 2;
+        for (int tile = 0; tile < n_tiles && ok; ++tile, ++gr) {
+          if (gr > 0) ok = xt_wait(&bars.tmem_gu_free, (gr - 1) & 1, abort_flag);
+          for (int m = 0; m < 2 && ok; ++m) {
+            const int nkb = fe.m[m].nslots >> 4;
+            for (int kb = 0; kb < nkb; ++kb, ++ri) {
+              const int slot = ri % XT_RING;
+              if (!(ok = xt_wait(&bars.w_full[slot], (ri / XT_RING) & 1, abort_flag))) break;
+              tc::fence_after_sync();
+              const uint64_t ad = tc::smem_desc_kmajor(ring_base + slot * XT_STAGE_BYTES, 2048, 128);
+              const uint64_t bd = tc::smem_desc_kmajor(act_base + m * act_m_bytes + (2 * kb) * (XT_NT * 16), XT_NT * 16, 128);
+              tc::mma_f16(m == 0 ? d_gate : d_up, ad, bd, idesc, kb > 0 ? 1u : 0u);
+              tc::mma_commit(&bars.w_empty[slot]);
+            }
+          }
+          if (!ok) break;
+          tc::mma_commit(&bars.gu_done);
+          ok = xt_wait(&bars.z_ready, gr & 1, abort_flag);
+          for (int mt = 0; mt < n_mt && ok; ++mt) {
+            for (int kb = 0; kb < 8; ++kb, ++ri) {
+              const int slot = ri % XT_RING;
+              if (!(ok = xt_wait(&bars.w_full[slot], (ri / XT_RING) & 1, abort_flag))) break;
+              tc::fence_after_sync();
+              const uint64_t ad = tc::smem_desc_kmajor(ring_base + slot * XT_STAGE_BYTES, 2048, 128);
+              const uint64_t bd = tc::smem_desc_kmajor(z_base + (2 * kb) * (XT_NT * 16), XT_NT * 16, 128);
+              tc::mma_f16(d_down + mt * XT_NT, ad, bd, idesc, (tile > 0 || kb > 0) ? 1u : 0u);
+              tc::mma_commit(&bars.w_empty[slot]);
+            }
+          }
+          if (ok) tc::mma_commit(&bars.down_done);
+        }
+      }
+    }
+    else if (warp >= XT_DQ_WARP0) {
+      // ------------------------------------------------------------------ dequantisers
+      const int dw = warp - XT_DQ_WARP0, tid_d = threadIdx.x - XT_DQ_WARP0 * 32;
+      const uint32_t act_m_bytes = static_cast<uint32_t>(XT_NT) * max_slots * 2;
+      // activation operand, once per item: act[m][chunk][n] = 8 consecutive contraction positions of token n
+      for (int m = 0; m < 2; ++m) {
+        const FastMat& fm = fe.m[m];
+        const int16_t* rank_t = reinterpret_cast<const int16_t*>(arena + fm.tab_off);
+        const __half* s_t = reinterpret_cast<const __half*>(arena + fm.tab_off + fm.nslots * 2);
+        const __half* h = m == 0 ? h_gate : h_up;
+        const int nchunks = fm.nslots >> 3;
+        for (int task = tid_d; task < nchunks * XT_NT; task += XT_DQ_WARPS * 32) {
+          const int n = task % XT_NT, c8 = task / XT_NT;
+          __half v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int q = (c8 & 1) * 8 + j;                      // position inside the 16-block
+            const int slot = (c8 >> 1) * 16 + ((q & 7) >> 1) + 8 * (q & 1) + ((q >> 3) << 2);
+            float val = 0.f;
+            if (n < n_tok) {
+              const int rk = rank_t[slot];
+              if (rk >= 0 && rk < h_rank) val = __half2float(h[static_cast<int64_t>(item.tok[n]) * h_rank + rk]) * __half2float(s_t[slot]);
+            }
+            v[j] = __float2half_rn(val);
+          }
+          *reinterpret_cast<uint4*>(sm.act + m * act_m_bytes + c8 * (XT_NT * 16) + (n >> 3) * 128 + (n & 7) * 16) =
+              *reinterpret_cast<uint4*>(v);
+        }
+      }
+      tc::fence_async_smem();
+      asm volatile("bar.sync 1, %0;" ::"n"(XT_DQ_WARPS * 32) : "memory");
+      if (tid_d == 0) tc::mbar_arrive(&bars.act_ready);
+
+      const int pair = dw >> 1, unit = lane + 32 * (dw & 1), x = unit >> 3, g = unit & 7;
+      uint32_t ri = ring_i, sr = sec_round;
+      bool ok = true;
+      for (int tile = 0; tile < n_tiles && ok; ++tile, ++sr) {
+        for (int m = 0; m < 2 && ok; ++m) {
+          ok = xt_wait(&bars.sec_full[m], sr & 1, abort_flag);
+          if (!ok) break;
+          const FastMat& fm = fe.m[m];
+          const uint32_t* words = reinterpret_cast<const uint32_t*>(sm.sec[m] + sec_scale_bytes);
+          const __half2* scale2 = reinterpret_cast<const __half2*>(sm.sec[m]);
+          int kb = 0;
+          for (int grp = 0; grp < 3 && ok; ++grp) {
+            const int b = group_bits(grp);
+            for (int i = 0; i < fm.nblk[grp]; ++i, ++kb, ++ri, words += 64 * b) {
+              if (static_cast<int>(ri & 3u) != pair) continue;
+              const int slot = ri % XT_RING;
+              if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
+              const uint32_t* w = words + (x * 8 + g) * b;
+              const __half2* sc = scale2 + kb * 8;
+              uint4 c0, c1, d0, d1;
+              if (b == 4) dequant_rowpair<4>(w, sc, sc, c0, c1, d0, d1);
+              else if (b == 3) dequant_rowpair<3>(w, sc, sc, c0, c1, d0, d1);
+              else dequant_rowpair<2>(w, sc, sc, c0, c1, d0, d1);
+              store_unit(sm.ring + slot * XT_STAGE_BYTES, x, g, c0, c1, d0, d1);
+              tc::fence_async_smem();
+              __syncwarp();
+              if (lane == 0) tc::mbar_arrive(&bars.w_full[slot]);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&bars.sec_empty[m]);
+        }
+        if (!ok) break;
+        ok = xt_wait(&bars.sec_full[2], sr & 1, abort_flag);
+        if (!ok) break;
+        const FastMat& fd = fe.m[2];
+        const uint32_t* dwords = reinterpret_cast<const uint32_t*>(sm.sec[2] + sec_scale_bytes);
+        const __half* scale_d = reinterpret_cast<const __half*>(sm.sec[2]);
+        for (int mt = 0; mt < n_mt && ok; ++mt) {
+          const int mb = 8 * mt + x;
+          int b = 0, boff = 0;
+          if (mb < nblk_d) {
+            if (mb < fd.nblk[0]) { b = 4; boff = mb * 256; }
+            else if (mb < fd.nblk[0] + fd.nblk[1]) { b = 3; boff = fd.nblk[0] * 256 + (mb - fd.nblk[0]) * 192; }
+            else { b = 2; boff = fd.nblk[0] * 256 + fd.nblk[1] * 192 + (mb - fd.nblk[0] - fd.nblk[1]) * 128; }
+          }
+          __half2 sg[8], sh[8];
+          if (b) {
+            const __half a = scale_d[16 * mb + g], c = scale_d[16 * mb + g + 8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { sg[i] = __halves2half2(a, a); sh[i] = __halves2half2(c, c); }
+          }
+          for (int kb = 0; kb < 8; ++kb, ++ri) {
+            if (static_cast<int>(ri & 3u) != pair) continue;
+            const int slot = ri % XT_RING;
+            if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
+            if (b) {
+              const uint32_t* w = dwords + boff + (kb * 8 + g) * b;
+              uint4 c0, c1, d0, d1;
+              if (b == 4) dequant_rowpair<4>(w, sg, sh, c0, c1, d0, d1);
+              else if (b == 3) dequant_rowpair<3>(w, sg, sh, c0, c1, d0, d1);
+              else dequant_rowpair<2>(w, sg, sh, c0, c1, d0, d1);
+              store_unit(sm.ring + slot * XT_STAGE_BYTES, x, g, c0, c1, d0, d1);
+            } else {
+              const uint4 zero = make_uint4(0, 0, 0, 0);
+              store_unit(sm.ring + slot * XT_STAGE_BYTES, x, g, zero, zero, zero, zero);
+            }
+            tc::fence_async_smem();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&bars.w_full[slot]);
+          }
+        }
+        __syncwarp();
+        if (ok && lane == 0) tc::mbar_arrive(&bars.sec_empty[2]);
+      }
+    } else {
+      // ------------------------------------------------------------------ epilogue warps 0-3
+      const int q = warp;
+      const uint32_t lane_sel = static_cast<uint32_t>(32 * q) << 16;
+      uint32_t gr = gu_round;
+      bool ok = true;
+      const int c = 32 * q + lane;                                   // row of D_g / D_u = column of the tile
+      const int c_pos = (c & ~15) + kperm16(c & 15);
+      unsigned char* zrow = sm.z + (c_pos >> 3) * (XT_NT * 16) + (c_pos & 7) * 2;
+      for (int tile = 0; tile < n_tiles && ok; ++tile, ++gr) {
+        ok = xt_wait(&bars.gu_done, gr & 1, abort_flag);
+        if (ok && gr > 0) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_sync();
+#pragma unroll 1
+        for (int n0 = 0; n0 < XT_NT; n0 += 32) {
+          float gv[32], uv[32];
+          tc::tmem_ld32(d_gate + lane_sel + n0, gv);
+          tc::tmem_ld32(d_up + lane_sel + n0, uv);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int n = n0 + i;
+            const float zf = (gv[i] / (1.f + __expf(-gv[i]))) * uv[i];
+            *reinterpret_cast<__half*>(zrow + (n >> 3) * 128 + (n & 7) * 16) = __float2half_rn(n < n_tok ? zf : 0.f);
+          }
+        }
+        tc::fence_before_sync();
+        tc::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) { tc::mbar_arrive(&bars.tmem_gu_free); tc::mbar_arrive(&bars.z_ready); }
+      }
+      if (ok) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag);
+      if (ok) {
+        tc::fence_after_sync();
+        const FastMat& fd = fe.m[2];
+        const int16_t* rank_d = reinterpret_cast<const int16_t*>(arena + fd.tab_off);
+        const __half* s_d = reinterpret_cast<const __half*>(arena + fd.tab_off + fd.nslots * 2);
+        for (int mt = 0; mt < n_mt; ++mt) {
+          const int slot = 128 * mt + 32 * q + lane;
+          int rk = -1;
+          float sv = 0.f;
+          if (slot < fd.nslots) { rk = rank_d[slot]; sv = __half2float(s_d[slot]); }
+          const bool live = rk >= 0 && rk < rank_out;
+#pragma unroll 1
+          for (int n0 = 0; n0 < XT_NT; n0 += 32) {
+            float v[32];
+            tc::tmem_ld32(d_down + mt * XT_NT + lane_sel + n0, v);
+            if (live) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int n = n0 + i;
+                if (n < n_tok) atomicAdd(&rank_accum[static_cast<int64_t>(item.tok[n]) * rank_out + rk], v[i] * sv * item.rw[n]);
+              }
+            }
+          }
+        }
+        tc::fence_before_sync();
+      }
+    }
+    // every role advances the shared counters identically
+    gu_round += n_tiles;
+    sec_round += n_tiles;
+    ring_i += static_cast<uint32_t>(n_tiles) * ((fe.m[0].nslots >> 4) + (fe.m[1].nslots >> 4) + n_mt * 8);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem_base, 512);
+  if (threadIdx.x == 0 && abort_flag_s) atomicExch(status, BM_ERR_TIMEOUT);
+}
+
+int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
+                      const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st) {
+  BM_REQUIRE(L->num_experts <= XT_MAX_E, BM_ERR_UNSUPPORTED, "experts_tc: more than %d experts", XT_MAX_E);
+  BM_REQUIRE(L->intermediate % N_TILE == 0, BM_ERR_UNSUPPORTED, "experts_tc: intermediate size must be a multiple of %d", N_TILE);
+  BM_REQUIRE(L->max_slots <= 3 * 128, BM_ERR_UNSUPPORTED, "experts_tc: %d row slots exceed the tensor-memory budget", L->max_slots);
+  const size_t smem = xt_smem_bytes(L->max_slots, L->max_words, L->num_experts);
+  BM_REQUIRE(smem <= 224 * 1024, BM_ERR_UNSUPPORTED, "experts_tc: layer needs %zu bytes of shared memory", smem);
+  static int attr_set_for = -1;
+  static int sm_count = 148;
+  if (attr_set_for != L->device) {
+    BM_CUDA(cudaFuncSetAttribute(experts_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+    BM_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, L->device));
+    attr_set_for = L->device;
+  }
+  experts_tc_kernel<<<sm_count, XT_THREADS, smem, st>>>(
+      L->fast_dev, static_cast<const unsigned char*>(L->arena), h_gate, h_up, L->rank_in, token_indices, expert_offsets,
+      route_w, L->rank_out, T, L->num_experts, L->n_tiles, L->max_slots, L->max_words, rank_accum, L->status_dev);
+  BM_LAUNCH_CHECK("experts_tc_kernel");
+  return BM_OK;
+}
+
+}  // namespace bm

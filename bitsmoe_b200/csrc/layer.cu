@@ -51,6 +51,8 @@ size_t fast_build_scratch_bytes(const FastPlan& P);
 int launch_arena_decode(const bm_layer* L, int e, int w, int8_t* codes, cudaStream_t st);
 int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                           const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
+int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
+                      const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
 int launch_experts_generic(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                            const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum,
                            cudaStream_t st);
@@ -314,6 +316,7 @@ extern "C" int bm_layer_create(const bm_layer_desc_t* desc, void* arena, size_t 
     L->fast_dev = reinterpret_cast<const FastExpert*>(static_cast<unsigned char*>(arena) + P.table_off);
     L->max_unit_bytes = P.max_unit_bytes;
     L->max_slots = P.max_slots;
+    L->max_words = P.max_words;
     rc = build_fast(L, P, st);
     if (rc) { delete L; return rc; }
     L->fast_ok = true;
@@ -425,7 +428,11 @@ extern "C" int bm_experts_forward(const bm_layer_t* L, const uint16_t* h_gate, c
   if (num_assign == 0 || L->num_experts == 0) return BM_OK;
   BM_REQUIRE(h_gate && h_up && token_indices && expert_offsets && route_weights, BM_ERR_INVALID_ARG,
              "experts_forward: null pointer");
-  BM_REQUIRE(path != BM_PATH_TENSOR, BM_ERR_UNSUPPORTED, "experts_forward: the tensor path is not available");
+  BM_REQUIRE(path != BM_PATH_TENSOR || L->fast_ok, BM_ERR_UNSUPPORTED,
+             "experts_forward: the tensor path needs 2/3/4-bit rows and full tiles; this layer has neither");
+  if (L->fast_ok && (path == BM_PATH_TENSOR || (path == BM_PATH_AUTO && num_assign > 16 * L->num_experts && !getenv("BM_NO_TC"))))
+    return launch_experts_tc(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up), token_indices,
+                             expert_offsets, route_weights, T, rank_accum, st);
   BM_REQUIRE(path != BM_PATH_DECODE || L->fast_ok, BM_ERR_UNSUPPORTED,
              "experts_forward: the decode path needs 2/3/4-bit rows and full tiles; this layer has neither");
   if (L->fast_ok && path != BM_PATH_GENERIC)

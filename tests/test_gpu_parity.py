@@ -296,3 +296,21 @@ def test_tensor_core_basis_products_vs_oracle(q30_small, T):
     packed.check_status()
     want = oforward.down_basis(acc, layer.u_down.cpu(), torch.float32) + res.float()
     helpers.assert_close(y, want, rtol=1e-2, atol=1e-2, what="down basis + residual (tcgen05)")
+
+
+@pytest.mark.parametrize("T", [5, 64, 200, 1000])
+def test_tensor_path_vs_oracle(q30_small, T):
+    """Fused mixed-bit grouped GEMM on tcgen05: weights as the 128-row operand, up to 64 assignments per item."""
+    layer, packed, experts = q30_small
+    x, logits = _inputs(layer, T, 80 + T)
+    if T == 1000:
+        logits = synth.router_logits(layer.cfg, T, seed=3, zipf_s=1.1)    # unbalanced experts, many items per expert
+    o = oforward.layer_forward(x, logits, layer.vh_gate.cpu(), layer.vh_up.cpu(), layer.u_down.cpu(), experts,
+                               layer.cfg.top_k)
+    args = [o[k].to(DEV) for k in ("h_gate", "h_up", "token_indices", "expert_offsets", "route_flat")]
+    got = packed.experts_forward(*args, path=capi.PATH_TENSOR)
+    packed.check_status()
+    helpers.assert_close(got, o["rank_accum"], rtol=1e-2, atol=3e-4, what="rank_accum (tensor path) vs fp32 oracle")
+    faithful = oforward.packed_forward(o["h_gate"], o["h_up"], o["token_indices"], o["expert_offsets"], o["route_flat"],
+                                       experts, layer.cfg.rank, mode="faithful")
+    helpers.assert_close(got, faithful, rtol=1e-2, atol=3e-4, what="rank_accum (tensor path) vs fp16-faithful oracle")
