@@ -3,8 +3,8 @@
 //   h_gate / h_up = x . Vh^T  (bitsmoe/models/qwen3moe/bitsmoe_block.py:63-64)
 //   y = fp16(rank_accum) . U_down^T (+ residual)  (bitsmoe/models/base_block.py:414)
 // One CTA computes a 128 x 256 tile: tokens on the 128 TMEM lanes, 256 fp32 accumulator columns.
-// All 8 warps stream K in slices of 64: global -> registers (converted to fp16 on the way) -> shared
-// memory in the K-major canonical layout of 8x16-byte core matrices; one elected thread issues
+// All 8 warps stream K in slices of 64 through a 4-stage ring (cp.async for fp16 data, registers + rounding for
+// bf16 / fp32 activations) into shared memory in the K-major canonical layout of 8x16-byte core matrices; one elected thread issues
 // tcgen05.mma (M=128, N=256, K=16) four times per slice and commits to the slice's mbarrier, so the
 // next slice is being loaded while the tensor core works on this one.  The epilogue reads the
 // accumulators with tcgen05.ld and stores rows of C.
@@ -13,7 +13,7 @@
 
 namespace bm {
 
-constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_THREADS = 256, TC_STAGES = 2;
+constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_THREADS = 256, TC_STAGES = 4, TC_AHEAD = 3;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;   // 32 KB
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
@@ -28,32 +28,24 @@ struct GemmTcArgs {
   int* status;
 };
 
-// 8 consecutive K elements of row r, chunk kc, converted to fp16 and returned as one 16-byte vector
-__device__ __forceinline__ uint4 load_chunk_f16(const void* base, int dtype, size_t elem) {
-  if (dtype == BM_F16) return *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(base) + elem);
-  __half out[8];
-  if (dtype == BM_BF16) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem);
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      out[2 * i] = __float2half_rn(__uint_as_float(w[i] << 16));
-      out[2 * i + 1] = __float2half_rn(__uint_as_float(w[i] & 0xffff0000u));
-    }
-  } else {
-    const float4 f0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem);
-    const float4 f1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem + 4);
-    out[0] = __float2half_rn(f0.x); out[1] = __float2half_rn(f0.y); out[2] = __float2half_rn(f0.z); out[3] = __float2half_rn(f0.w);
-    out[4] = __float2half_rn(f1.x); out[5] = __float2half_rn(f1.y); out[6] = __float2half_rn(f1.z); out[7] = __float2half_rn(f1.w);
-  }
-  return *reinterpret_cast<uint4*>(out);
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t dst = tc::smem_u32(smem);
+  const int bytes = valid ? 16 : 0;   // src-size 0 zero-fills the 16 bytes
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // canonical K-major tile of `rows` rows x 64 K: chunk kc (8 K elements) of row r lives at
 //   kc * rows * 16 + (r / 8) * 128 + (r % 8) * 16
 __device__ __forceinline__ uint32_t canon_off(int rows, int r, int kc) { return kc * rows * 16 + (r >> 3) * 128 + (r & 7) * 16; }
 
-__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(GemmTcArgs a) {
+// XD = BM_F16: activations go to shared memory untouched with cp.async.  XD = BM_BF16 / BM_F32: they are loaded
+// to registers (all loads of a slice first), rounded to fp16 and stored; both MMA operands are always fp16
+// (an instruction descriptor that mixed a bf16 A with an fp16 B raised "illegal instruction" on a B200).
+template <int XD>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmTcArgs a) {
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   __shared__ __align__(8) uint64_t bar_free[TC_STAGES];   // MMAs that read stage s are complete
   __shared__ __align__(8) uint64_t bar_done;              // all MMAs of the tile are complete
@@ -76,33 +68,80 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(GemmTcArgs a) {
   bool ok = true;
   // lane -> (row within an 8-row group, one of 4 chunks): a quarter warp fills one 128-byte core matrix
   const int r8 = lane & 7, kq = lane >> 3;
-  for (int s = 0; s < nslices; ++s) {
+
+  auto issue_slice = [&](int s) {
     const int buf = s % TC_STAGES;
     unsigned char* As = tc_smem + buf * TC_STAGE_BYTES;
     unsigned char* Bs = As + TC_A_BYTES;
-    if (s >= TC_STAGES && !tc::mbar_wait(&bar_free[buf], ((s / TC_STAGES) - 1) & 1)) { ok = false; break; }
     const int k0 = s * TC_BK;
-    // A: 128 rows x 8 chunks = 1024 vectors; B: 256 rows x 8 chunks = 2048 vectors; 32 vectors per warp step
-    for (int v = warp; v < (TC_BM + TC_BN) / 8 * 2; v += TC_THREADS / 32) {
-      // v enumerates (8-row group, pair of 4-chunk halves)
-      const int grp = v >> 1, kc = (v & 1) * 4 + kq;
-      if (grp < TC_BM / 8) {
-        const int r = grp * 8 + r8;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (m0 + r < a.M) val = load_chunk_f16(a.X, a.x_dtype, static_cast<size_t>(m0 + r) * a.K + k0 + kc * 8);
-        *reinterpret_cast<uint4*>(As + canon_off(TC_BM, r, kc)) = val;
-      } else {
-        const int r = (grp - TC_BM / 8) * 8 + r8;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (n0 + r < a.N) val = *reinterpret_cast<const uint4*>(W + static_cast<size_t>(n0 + r) * a.K + k0 + kc * 8);
-        *reinterpret_cast<uint4*>(Bs + canon_off(TC_BN, r, kc)) = val;
+    if (XD == BM_F16) {
+      const uint16_t* X = reinterpret_cast<const uint16_t*>(a.X);
+#pragma unroll
+      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
+        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+        const bool valid = m0 + r < a.M;
+        cp_async16(As + canon_off(TC_BM, r, kc), X + static_cast<size_t>(valid ? m0 + r : 0) * a.K + k0 + kc * 8, valid);
+      }
+    } else if (XD == BM_BF16) {
+      const uint16_t* X = reinterpret_cast<const uint16_t*>(a.X);
+      uint4 raw[(TC_BM / 8 * 2) / (TC_THREADS / 32)];
+#pragma unroll
+      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
+        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+        raw[i] = make_uint4(0, 0, 0, 0);
+        if (m0 + r < a.M) raw[i] = *reinterpret_cast<const uint4*>(X + static_cast<size_t>(m0 + r) * a.K + k0 + kc * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
+        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+        __half2 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xffff0000u));
+        *reinterpret_cast<uint4*>(As + canon_off(TC_BM, r, kc)) = *reinterpret_cast<uint4*>(h);
+      }
+    } else {
+      const float* X = reinterpret_cast<const float*>(a.X);
+      float4 f[(TC_BM / 8 * 2) / (TC_THREADS / 32)][2];
+#pragma unroll
+      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
+        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+        if (m0 + r < a.M) {
+          const float* src = X + static_cast<size_t>(m0 + r) * a.K + k0 + kc * 8;
+          f[i][0] = *reinterpret_cast<const float4*>(src);
+          f[i][1] = *reinterpret_cast<const float4*>(src + 4);
+        } else {
+          f[i][0] = f[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
+        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+        __half2 h[4] = {__floats2half2_rn(f[i][0].x, f[i][0].y), __floats2half2_rn(f[i][0].z, f[i][0].w),
+                        __floats2half2_rn(f[i][1].x, f[i][1].y), __floats2half2_rn(f[i][1].z, f[i][1].w)};
+        *reinterpret_cast<uint4*>(As + canon_off(TC_BM, r, kc)) = *reinterpret_cast<uint4*>(h);
       }
     }
+#pragma unroll
+    for (int i = 0; i < (TC_BN / 8 * 2) / (TC_THREADS / 32); ++i) {
+      const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+      const bool valid = n0 + r < a.N;
+      cp_async16(Bs + canon_off(TC_BN, r, kc), W + static_cast<size_t>(valid ? n0 + r : 0) * a.K + k0 + kc * 8, valid);
+    }
+  };
+
+  for (int s = 0; s < TC_AHEAD; ++s) {
+    if (s < nslices) issue_slice(s);
+    cp_async_commit();
+  }
+  for (int s = 0; s < nslices; ++s) {
+    const int buf = s % TC_STAGES;
+    cp_async_wait<TC_AHEAD - 1>();     // this thread's copies of slice s have landed
     tc::fence_async_smem();
     __syncthreads();
     if (threadIdx.x == 0) {
       tc::fence_after_sync();
-      const uint32_t a_base = tc::smem_u32(As), b_base = tc::smem_u32(Bs);
+      const uint32_t a_base = tc::smem_u32(tc_smem + buf * TC_STAGE_BYTES), b_base = a_base + TC_A_BYTES;
 #pragma unroll
       for (int kk = 0; kk < TC_BK / 16; ++kk) {
         const uint64_t ad = tc::smem_desc_kmajor(a_base + 2 * kk * TC_BM * 16, TC_BM * 16, 128);
@@ -112,7 +151,15 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(GemmTcArgs a) {
       tc::mma_commit(&bar_free[buf]);
       if (s == nslices - 1) tc::mma_commit(&bar_done);
     }
+    const int nxt = s + TC_AHEAD;
+    if (nxt < nslices && ok) {
+      // stage nxt % STAGES was last read by the MMAs of slice nxt - STAGES = s - 1
+      if (nxt >= TC_STAGES && !tc::mbar_wait(&bar_free[nxt % TC_STAGES], ((nxt / TC_STAGES) - 1) & 1)) ok = false;
+      if (ok) issue_slice(nxt);
+    }
+    cp_async_commit();
   }
+  cp_async_wait<0>();
   if (ok && !tc::mbar_wait(&bar_done, 0)) ok = false;
   tc::fence_after_sync();
   if (ok) {
@@ -123,8 +170,34 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(GemmTcArgs a) {
     for (int c = 0; c < TC_BN / 2; c += 32) {
       float v[32];
       tc::tmem_ld32(tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + col_half + c, v);
-      if (row < a.M) {
-        const int n = n0 + col_half + c;
+      const int n = n0 + col_half + c;
+      if (row < a.M && n + 32 <= a.N) {
+        const size_t idx = static_cast<size_t>(row) * a.N + n;
+        if (a.residual && z == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += load_act(a.residual, a.c_dtype, idx + i);
+        }
+        if (a.c_dtype == BM_F32) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.C[z]) + idx + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        } else {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (a.c_dtype == BM_F16) {
+              const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+              pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+              pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          }
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.C[z]) + idx);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+        }
+      } else if (row < a.M) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           if (n + i < a.N) {
@@ -147,14 +220,19 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(GemmTcArgs a) {
 int launch_gemm_tc(const GemmTcArgs& a, int problems, cudaStream_t st) {
   BM_REQUIRE(a.K % TC_BK == 0, BM_ERR_UNSUPPORTED, "gemm_tc: K=%d must be a multiple of %d", a.K, TC_BK);
   BM_REQUIRE((reinterpret_cast<uintptr_t>(a.X) & 15u) == 0, BM_ERR_UNSUPPORTED, "gemm_tc: activations must be 16-byte aligned");
+  BM_REQUIRE(a.N % 8 == 0, BM_ERR_UNSUPPORTED, "gemm_tc: N=%d must be a multiple of 8", a.N);
   static bool attr_done = false;
   const int smem = TC_STAGES * TC_STAGE_BYTES;
   if (!attr_done) {
-    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_done = true;
   }
   dim3 grid((a.M + TC_BM - 1) / TC_BM, (a.N + TC_BN - 1) / TC_BN, problems);
-  gemm_tc_kernel<<<grid, TC_THREADS, smem, st>>>(a);
+  if (a.x_dtype == BM_F32) gemm_tc_kernel<BM_F32><<<grid, TC_THREADS, smem, st>>>(a);
+  else if (a.x_dtype == BM_BF16) gemm_tc_kernel<BM_BF16><<<grid, TC_THREADS, smem, st>>>(a);
+  else gemm_tc_kernel<BM_F16><<<grid, TC_THREADS, smem, st>>>(a);
   BM_LAUNCH_CHECK("gemm_tc_kernel");
   return BM_OK;
 }
