@@ -6,14 +6,14 @@
 //   gate/up:  D_g[c, n] = sum_slot  W_g[c, slot] * act_g[n, slot]      (M = 128 columns c, N = 64 tokens)
 //   down:     D_d[slot, n] += sum_c W_d[slot, c] * z[n, c]             (M = 128 row slots x 3, N = 64 tokens)
 // so decode-like small N and prefill share one tile shape, and D_d accumulates over all tiles in TMEM.
-// Warp roles (448 threads):
-//   warps 0-3   epilogue: tcgen05.ld D_g/D_u -> z = silu(g)*u -> fp16 Z tile in shared memory; at the end of
+// Warp roles (576 threads):
+//   warps 0-7   epilogue (two per TMEM lane quarter, 32 token columns each): tcgen05.ld D_g/D_u -> z = silu(g)*u -> fp16 Z tile in shared memory; at the end of
 //               the item D_d -> * s * route weight -> fp32 atomics into rank_accum
-//   warp  4     producer: item descriptor, cp.async.bulk of the packed words + scales of (tile, matrix)
+//   warp  8     producer: item descriptor, cp.async.bulk of the packed words + scales of (tile, matrix)
 //               sections into a 3-slot ring
-//   warp  5     MMA issue (one thread) and tcgen05.commit to the ring / phase mbarriers
-//   warps 6-13  dequantisers: bit-plane words -> fp16 (q * scale) A-operand stages of 128 rows x 16 K in the
-//               canonical K-major core-matrix layout, 8-stage ring; they also build the activation operand
+//   warp  9     MMA issue (one thread) and tcgen05.commit to the ring / phase mbarriers
+//   warps 10-17 dequantisers: bit-plane words -> fp16 (q * scale) A-operand stages of 128 rows x 16 K in the
+//               canonical K-major core-matrix layout, 4-stage ring of 4 blocks; they also build the activation operand
 //               act[n, slot] = fp16(h[token, rank(slot)] * s(slot)) once per item
 // Every mbarrier wait is bounded in time and aborts the whole CTA through a shared flag.
 #include "fast_layout.cuh"
@@ -21,11 +21,28 @@
 
 namespace bm {
 
+// Optional per-role phase timing (debug builds): cycles accumulated into status[8 + 2*slot] as uint64.
+#ifdef BM_TC_TIMING
+#define XT_TICK_INIT() long long xt_t_ = clock64()
+#define XT_TICK(slot)                                                                                  \
+  do {                                                                                                 \
+    const long long now_ = clock64();                                                                  \
+    atomicAdd(reinterpret_cast<unsigned long long*>(status + 8) + (slot), static_cast<unsigned long long>(now_ - xt_t_)); \
+    xt_t_ = now_;                                                                                      \
+  } while (0)
+#else
+#define XT_TICK_INIT() do {} while (0)
+#define XT_TICK(slot) do {} while (0)
+#endif
+
 constexpr int XT_NT = 64;                 // tokens (assignments) per item = MMA N
-constexpr int XT_THREADS = 448;
-constexpr int XT_EPI_WARPS = 4, XT_PRODUCER_WARP = 4, XT_MMA_WARP = 5, XT_DQ_WARP0 = 6, XT_DQ_WARPS = 8;
-constexpr int XT_RING = 8;                // A-operand stages
-constexpr int XT_STAGE_BYTES = 128 * 16 * 2;
+constexpr int XT_THREADS = 576;
+constexpr int XT_EPI_WARPS = 8, XT_PRODUCER_WARP = 8, XT_MMA_WARP = 9, XT_DQ_WARP0 = 10, XT_DQ_WARPS = 8;
+constexpr int XT_RING = 4;                // A-operand stages
+constexpr int XT_STAGE_BLOCKS = 4;        // contraction blocks of 16 per stage (one per dequantiser warp pair)
+constexpr int XT_BLOCK_BYTES = 128 * 16 * 2;
+constexpr int XT_STAGE_BYTES = XT_STAGE_BLOCKS * XT_BLOCK_BYTES;
+constexpr int XT_CHUNK_STRIDE = XT_NT * 16 + 16;   // bytes between 8-position chunks of the token-side operands (padded: conflict-free stores)
 constexpr int XT_MAX_E = 1024;
 
 struct XtBars {
@@ -109,6 +126,8 @@ struct XtSmem {
   unsigned char* ring;    // [XT_RING][XT_STAGE_BYTES]
   unsigned char* sec[3];  // section buffers: [scale (sec_scale_bytes) | words]
   int* prefix;            // [E + 1] items before each expert
+  int16_t* rank_s;        // [2][max_slots] logical rank per slot (gate, up) of the current item's expert
+  __half* s_s;            // [2][max_slots]
 };
 
 __host__ __device__ inline size_t xt_sec_bytes(int max_slots, int max_words) {
@@ -116,11 +135,12 @@ __host__ __device__ inline size_t xt_sec_bytes(int max_slots, int max_words) {
 }
 __host__ __device__ inline size_t xt_smem_bytes(int max_slots, int max_words, int num_experts) {
   size_t o = 0;
-  o += static_cast<size_t>(2) * XT_NT * max_slots * 2;      // act
-  o += static_cast<size_t>(XT_NT) * N_TILE * 2;             // z
-  o += static_cast<size_t>(XT_RING) * XT_STAGE_BYTES;       // ring
+  o += static_cast<size_t>(2) * (max_slots / 8) * XT_CHUNK_STRIDE;   // act
+  o += static_cast<size_t>(N_TILE / 8) * XT_CHUNK_STRIDE;            // z
+  o = align_up_c(o, 128) + static_cast<size_t>(XT_RING) * XT_STAGE_BYTES;       // ring
   o += 3 * xt_sec_bytes(max_slots, max_words);
   o += align_up_c(static_cast<size_t>(num_experts + 1) * 4, 128);
+  o += align_up_c(static_cast<size_t>(2) * max_slots * 4, 128);
   return o + 1024;                                          // slack for the 1024-byte base alignment
 }
 
@@ -140,16 +160,19 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
   {
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(xt_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     size_t o = 0;
-    sm.act = base; o += static_cast<size_t>(2) * XT_NT * max_slots * 2;
-    sm.z = base + o; o += static_cast<size_t>(XT_NT) * N_TILE * 2;
+    sm.act = base; o += static_cast<size_t>(2) * (max_slots / 8) * XT_CHUNK_STRIDE;
+    sm.z = base + o; o += static_cast<size_t>(N_TILE / 8) * XT_CHUNK_STRIDE;
+    o = align_up_c(o, 128);
     sm.ring = base + o; o += static_cast<size_t>(XT_RING) * XT_STAGE_BYTES;
     for (int i = 0; i < 3; ++i) { sm.sec[i] = base + o; o += xt_sec_bytes(max_slots, max_words); }
-    sm.prefix = reinterpret_cast<int*>(base + o);
+    sm.prefix = reinterpret_cast<int*>(base + o); o += align_up_c(static_cast<size_t>(num_experts + 1) * 4, 128);
+    sm.rank_s = reinterpret_cast<int16_t*>(base + o);
+    sm.s_s = reinterpret_cast<__half*>(base + o + static_cast<size_t>(2) * max_slots * 2);
   }
   const size_t sec_scale_bytes = align_up_c(static_cast<size_t>(max_slots) * 2, 128);
   if (threadIdx.x == 0) {
     for (int i = 0; i < 3; ++i) { tc::mbar_init(&bars.sec_full[i], 1); tc::mbar_init(&bars.sec_empty[i], XT_DQ_WARPS); }
-    for (int i = 0; i < XT_RING; ++i) { tc::mbar_init(&bars.w_full[i], 2); tc::mbar_init(&bars.w_empty[i], 1); }
+    for (int i = 0; i < XT_RING; ++i) { tc::mbar_init(&bars.w_full[i], XT_DQ_WARPS); tc::mbar_init(&bars.w_empty[i], 1); }
     tc::mbar_init(&bars.act_ready, 1);
     tc::mbar_init(&bars.gu_done, 1);
     tc::mbar_init(&bars.z_ready, XT_EPI_WARPS);
@@ -228,75 +251,108 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
     } else if (warp == XT_MMA_WARP) {
       // ------------------------------------------------------------------ MMA issue
       if (lane == 0) {
+        XT_TICK_INIT();
         bool ok = xt_wait(&bars.act_ready, item_round & 1, abort_flag);
+        XT_TICK(0);
         uint32_t ri = ring_i, gr = gu_round;
         const uint32_t act_base = tc::smem_u32(sm.act), z_base = tc::smem_u32(sm.z), ring_base = tc::smem_u32(sm.ring);
-        const uint32_t act_m_bytes = static_cast<uint32_t>(XT_NT) * max_slots * 2;
+        const uint32_t act_m_bytes = static_cast<uint32_t>(max_slots / 8) * XT_CHUNK_STRIDE;
+        // descriptors: constant upper part, start-address field advanced per block
+        const uint64_t a_desc0 = tc::smem_desc_kmajor(ring_base, 2048, 128);
+        const uint64_t b_desc0 = tc::smem_desc_kmajor(act_base, XT_CHUNK_STRIDE, 128);
+        const uint64_t z_desc0 = tc::smem_desc_kmajor(z_base, XT_CHUNK_STRIDE, 128);
         for (int tile = 0; tile < n_tiles && ok; ++tile, ++gr) {
           if (gr > 0) ok = xt_wait(&bars.tmem_gu_free, (gr - 1) & 1, abort_flag);
+          XT_TICK(1);
           for (int m = 0; m < 2 && ok; ++m) {
             const int nkb = fe.m[m].nslots >> 4;
-            for (int kb = 0; kb < nkb; ++kb, ++ri) {
+            const uint64_t bm_desc = b_desc0 + ((m * act_m_bytes) >> 4);
+            for (int kb0 = 0; kb0 < nkb; kb0 += XT_STAGE_BLOCKS, ++ri) {
               const int slot = ri % XT_RING;
               if (!(ok = xt_wait(&bars.w_full[slot], (ri / XT_RING) & 1, abort_flag))) break;
               tc::fence_after_sync();
-              const uint64_t ad = tc::smem_desc_kmajor(ring_base + slot * XT_STAGE_BYTES, 2048, 128);
-              const uint64_t bd = tc::smem_desc_kmajor(act_base + m * act_m_bytes + (2 * kb) * (XT_NT * 16), XT_NT * 16, 128);
-              tc::mma_f16(m == 0 ? d_gate : d_up, ad, bd, idesc, kb > 0 ? 1u : 0u);
+              const int cnt = min(XT_STAGE_BLOCKS, nkb - kb0);
+              for (int j = 0; j < cnt; ++j) {
+                const uint64_t ad = a_desc0 + ((slot * XT_STAGE_BYTES + j * XT_BLOCK_BYTES) >> 4);
+                const uint64_t bd = bm_desc + ((2 * (kb0 + j) * XT_CHUNK_STRIDE) >> 4);
+                tc::mma_f16(m == 0 ? d_gate : d_up, ad, bd, idesc, (kb0 + j) > 0 ? 1u : 0u);
+              }
               tc::mma_commit(&bars.w_empty[slot]);
             }
           }
           if (!ok) break;
+          XT_TICK(2);
           tc::mma_commit(&bars.gu_done);
           ok = xt_wait(&bars.z_ready, gr & 1, abort_flag);
+          XT_TICK(3);
           for (int mt = 0; mt < n_mt && ok; ++mt) {
-            for (int kb = 0; kb < 8; ++kb, ++ri) {
+            for (int kb0 = 0; kb0 < 8; kb0 += XT_STAGE_BLOCKS, ++ri) {
               const int slot = ri % XT_RING;
               if (!(ok = xt_wait(&bars.w_full[slot], (ri / XT_RING) & 1, abort_flag))) break;
               tc::fence_after_sync();
-              const uint64_t ad = tc::smem_desc_kmajor(ring_base + slot * XT_STAGE_BYTES, 2048, 128);
-              const uint64_t bd = tc::smem_desc_kmajor(z_base + (2 * kb) * (XT_NT * 16), XT_NT * 16, 128);
-              tc::mma_f16(d_down + mt * XT_NT, ad, bd, idesc, (tile > 0 || kb > 0) ? 1u : 0u);
+              for (int j = 0; j < XT_STAGE_BLOCKS; ++j) {
+                const uint64_t ad = a_desc0 + ((slot * XT_STAGE_BYTES + j * XT_BLOCK_BYTES) >> 4);
+                const uint64_t bd = z_desc0 + ((2 * (kb0 + j) * XT_CHUNK_STRIDE) >> 4);
+                tc::mma_f16(d_down + mt * XT_NT, ad, bd, idesc, (tile > 0 || kb0 + j > 0) ? 1u : 0u);
+              }
               tc::mma_commit(&bars.w_empty[slot]);
             }
           }
           if (ok) tc::mma_commit(&bars.down_done);
+          XT_TICK(4);
         }
       }
     }
     else if (warp >= XT_DQ_WARP0) {
       // ------------------------------------------------------------------ dequantisers
       const int dw = warp - XT_DQ_WARP0, tid_d = threadIdx.x - XT_DQ_WARP0 * 32;
-      const uint32_t act_m_bytes = static_cast<uint32_t>(XT_NT) * max_slots * 2;
+      const uint32_t act_m_bytes = static_cast<uint32_t>(max_slots / 8) * XT_CHUNK_STRIDE;
+      XT_TICK_INIT();
       // activation operand, once per item: act[m][chunk][n] = 8 consecutive contraction positions of token n
       for (int m = 0; m < 2; ++m) {
         const FastMat& fm = fe.m[m];
         const int16_t* rank_t = reinterpret_cast<const int16_t*>(arena + fm.tab_off);
         const __half* s_t = reinterpret_cast<const __half*>(arena + fm.tab_off + fm.nslots * 2);
+        for (int i = tid_d; i < fm.nslots; i += XT_DQ_WARPS * 32) {
+          const int rk = rank_t[i];
+          const bool live = rk >= 0 && rk < h_rank;
+          sm.rank_s[m * max_slots + i] = static_cast<int16_t>(live ? rk : 0);
+          sm.s_s[m * max_slots + i] = live ? s_t[i] : __float2half(0.f);
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(XT_DQ_WARPS * 32) : "memory");
+      for (int m = 0; m < 2; ++m) {
+        const FastMat& fm = fe.m[m];
         const __half* h = m == 0 ? h_gate : h_up;
+        const int16_t* rk_s = sm.rank_s + m * max_slots;
+        const __half* sv_s = sm.s_s + m * max_slots;
         const int nchunks = fm.nslots >> 3;
+#pragma unroll 2
         for (int task = tid_d; task < nchunks * XT_NT; task += XT_DQ_WARPS * 32) {
-          const int n = task % XT_NT, c8 = task / XT_NT;
-          __half v[8];
+          const int n = task / nchunks, c8 = task % nchunks;
+          const __half* hrow = h + static_cast<int64_t>(item.tok[n]) * h_rank;
+          const float live = n < n_tok ? 1.f : 0.f;
+          int slot[8];
+          __half hv[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int q = (c8 & 1) * 8 + j;                      // position inside the 16-block
-            const int slot = (c8 >> 1) * 16 + ((q & 7) >> 1) + 8 * (q & 1) + ((q >> 3) << 2);
-            float val = 0.f;
-            if (n < n_tok) {
-              const int rk = rank_t[slot];
-              if (rk >= 0 && rk < h_rank) val = __half2float(h[static_cast<int64_t>(item.tok[n]) * h_rank + rk]) * __half2float(s_t[slot]);
-            }
-            v[j] = __float2half_rn(val);
+            slot[j] = (c8 >> 1) * 16 + ((q & 7) >> 1) + 8 * (q & 1) + ((q >> 3) << 2);
+            hv[j] = hrow[rk_s[slot[j]]];
           }
-          *reinterpret_cast<uint4*>(sm.act + m * act_m_bytes + c8 * (XT_NT * 16) + (n >> 3) * 128 + (n & 7) * 16) =
+          __half v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __float2half_rn(__half2float(hv[j]) * __half2float(sv_s[slot[j]]) * live);
+          *reinterpret_cast<uint4*>(sm.act + m * act_m_bytes + c8 * XT_CHUNK_STRIDE + (n >> 3) * 128 + (n & 7) * 16) =
               *reinterpret_cast<uint4*>(v);
         }
       }
       tc::fence_async_smem();
       asm volatile("bar.sync 1, %0;" ::"n"(XT_DQ_WARPS * 32) : "memory");
       if (tid_d == 0) tc::mbar_arrive(&bars.act_ready);
+      if (tid_d == 0) XT_TICK(5);
 
+      // warp pair `pair` converts block `pair` of every stage; `unit` = one row pair of that block per thread
       const int pair = dw >> 1, unit = lane + 32 * (dw & 1), x = unit >> 3, g = unit & 7;
       uint32_t ri = ring_i, sr = sec_round;
       bool ok = true;
@@ -304,27 +360,34 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         for (int m = 0; m < 2 && ok; ++m) {
           ok = xt_wait(&bars.sec_full[m], sr & 1, abort_flag);
           if (!ok) break;
+          if (tid_d == 0) XT_TICK(6);
           const FastMat& fm = fe.m[m];
           const uint32_t* words = reinterpret_cast<const uint32_t*>(sm.sec[m] + sec_scale_bytes);
           const __half2* scale2 = reinterpret_cast<const __half2*>(sm.sec[m]);
-          int kb = 0;
-          for (int grp = 0; grp < 3 && ok; ++grp) {
-            const int b = group_bits(grp);
-            for (int i = 0; i < fm.nblk[grp]; ++i, ++kb, ++ri, words += 64 * b) {
-              if (static_cast<int>(ri & 3u) != pair) continue;
-              const int slot = ri % XT_RING;
-              if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
-              const uint32_t* w = words + (x * 8 + g) * b;
+          const int nkb = fm.nslots >> 4;
+          const int e4 = fm.nblk[0], e3 = fm.nblk[0] + fm.nblk[1];
+          for (int kb0 = 0; kb0 < nkb; kb0 += XT_STAGE_BLOCKS, ++ri) {
+            const int slot = ri % XT_RING;
+            if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
+            if (tid_d == 0) XT_TICK(7);
+            const int kb = kb0 + pair;
+            if (kb < nkb) {
+              int b, boff;
+              if (kb < e4) { b = 4; boff = kb * 256; }
+              else if (kb < e3) { b = 3; boff = e4 * 256 + (kb - e4) * 192; }
+              else { b = 2; boff = e4 * 256 + (e3 - e4) * 192 + (kb - e3) * 128; }
+              const uint32_t* w = words + boff + (x * 8 + g) * b;
               const __half2* sc = scale2 + kb * 8;
               uint4 c0, c1, d0, d1;
               if (b == 4) dequant_rowpair<4>(w, sc, sc, c0, c1, d0, d1);
               else if (b == 3) dequant_rowpair<3>(w, sc, sc, c0, c1, d0, d1);
               else dequant_rowpair<2>(w, sc, sc, c0, c1, d0, d1);
-              store_unit(sm.ring + slot * XT_STAGE_BYTES, x, g, c0, c1, d0, d1);
+              store_unit(sm.ring + slot * XT_STAGE_BYTES + pair * XT_BLOCK_BYTES, x, g, c0, c1, d0, d1);
               tc::fence_async_smem();
-              __syncwarp();
-              if (lane == 0) tc::mbar_arrive(&bars.w_full[slot]);
             }
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&bars.w_full[slot]);
+            if (tid_d == 0) XT_TICK(8);
           }
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(&bars.sec_empty[m]);
@@ -349,20 +412,21 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
 #pragma unroll
             for (int i = 0; i < 8; ++i) { sg[i] = __halves2half2(a, a); sh[i] = __halves2half2(c, c); }
           }
-          for (int kb = 0; kb < 8; ++kb, ++ri) {
-            if (static_cast<int>(ri & 3u) != pair) continue;
+          for (int kb0 = 0; kb0 < 8; kb0 += XT_STAGE_BLOCKS, ++ri) {
             const int slot = ri % XT_RING;
             if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
+            const int kb = kb0 + pair;
+            unsigned char* dst = sm.ring + slot * XT_STAGE_BYTES + pair * XT_BLOCK_BYTES;
             if (b) {
               const uint32_t* w = dwords + boff + (kb * 8 + g) * b;
               uint4 c0, c1, d0, d1;
               if (b == 4) dequant_rowpair<4>(w, sg, sh, c0, c1, d0, d1);
               else if (b == 3) dequant_rowpair<3>(w, sg, sh, c0, c1, d0, d1);
               else dequant_rowpair<2>(w, sg, sh, c0, c1, d0, d1);
-              store_unit(sm.ring + slot * XT_STAGE_BYTES, x, g, c0, c1, d0, d1);
+              store_unit(dst, x, g, c0, c1, d0, d1);
             } else {
               const uint4 zero = make_uint4(0, 0, 0, 0);
-              store_unit(sm.ring + slot * XT_STAGE_BYTES, x, g, zero, zero, zero, zero);
+              store_unit(dst, x, g, zero, zero, zero, zero);
             }
             tc::fence_async_smem();
             __syncwarp();
@@ -374,27 +438,29 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
       }
     } else {
       // ------------------------------------------------------------------ epilogue warps 0-3
-      const int q = warp;
+      const int q = warp & 3, nhalf = (warp >> 2) * 32;      // lane quarter, first of this warp's 32 token columns
       const uint32_t lane_sel = static_cast<uint32_t>(32 * q) << 16;
       uint32_t gr = gu_round;
       bool ok = true;
+      XT_TICK_INIT();
       const int c = 32 * q + lane;                                   // row of D_g / D_u = column of the tile
       const int c_pos = (c & ~15) + kperm16(c & 15);
-      unsigned char* zrow = sm.z + (c_pos >> 3) * (XT_NT * 16) + (c_pos & 7) * 2;
+      unsigned char* zrow = sm.z + (c_pos >> 3) * XT_CHUNK_STRIDE + (c_pos & 7) * 2;
       for (int tile = 0; tile < n_tiles && ok; ++tile, ++gr) {
         ok = xt_wait(&bars.gu_done, gr & 1, abort_flag);
         if (ok && gr > 0) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag);
         if (!ok) break;
+        if (threadIdx.x == 0) XT_TICK(9);
         tc::fence_after_sync();
-#pragma unroll 1
-        for (int n0 = 0; n0 < XT_NT; n0 += 32) {
+        {
+          const int n0 = nhalf;
           float gv[32], uv[32];
           tc::tmem_ld32(d_gate + lane_sel + n0, gv);
           tc::tmem_ld32(d_up + lane_sel + n0, uv);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int n = n0 + i;
-            const float zf = (gv[i] / (1.f + __expf(-gv[i]))) * uv[i];
+            const float zf = __fdividef(gv[i] * uv[i], 1.f + __expf(-gv[i]));
             *reinterpret_cast<__half*>(zrow + (n >> 3) * 128 + (n & 7) * 16) = __float2half_rn(n < n_tok ? zf : 0.f);
           }
         }
@@ -402,8 +468,10 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         tc::fence_async_smem();
         __syncwarp();
         if (lane == 0) { tc::mbar_arrive(&bars.tmem_gu_free); tc::mbar_arrive(&bars.z_ready); }
+        if (threadIdx.x == 0) XT_TICK(10);
       }
       if (ok) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag);
+      if (threadIdx.x == 0) XT_TICK(11);
       if (ok) {
         tc::fence_after_sync();
         const FastMat& fd = fe.m[2];
@@ -415,8 +483,8 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
           float sv = 0.f;
           if (slot < fd.nslots) { rk = rank_d[slot]; sv = __half2float(s_d[slot]); }
           const bool live = rk >= 0 && rk < rank_out;
-#pragma unroll 1
-          for (int n0 = 0; n0 < XT_NT; n0 += 32) {
+          {
+            const int n0 = nhalf;
             float v[32];
             tc::tmem_ld32(d_down + mt * XT_NT + lane_sel + n0, v);
             if (live) {
@@ -430,11 +498,14 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         }
         tc::fence_before_sync();
       }
+      if (threadIdx.x == 0) XT_TICK(12);
     }
     // every role advances the shared counters identically
     gu_round += n_tiles;
     sec_round += n_tiles;
-    ring_i += static_cast<uint32_t>(n_tiles) * ((fe.m[0].nslots >> 4) + (fe.m[1].nslots >> 4) + n_mt * 8);
+    ring_i += static_cast<uint32_t>(n_tiles) * ((((fe.m[0].nslots >> 4) + XT_STAGE_BLOCKS - 1) / XT_STAGE_BLOCKS) +
+                                                (((fe.m[1].nslots >> 4) + XT_STAGE_BLOCKS - 1) / XT_STAGE_BLOCKS) +
+                                                n_mt * (8 / XT_STAGE_BLOCKS));
   }
   tc::fence_before_sync();
   __syncthreads();
