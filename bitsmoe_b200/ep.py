@@ -1,0 +1,168 @@
+"""Expert parallelism for one packed MoE layer: one process per GPU, experts sharded, tokens data-parallel.
+
+The reference has no distributed code (its only multi-GPU mechanism is HF ``device_map`` placement,
+bitsmoe/evaluation/ppl_eval.py:321-327); this module adds the exchange that sharding the experts of
+bitsmoe/models/base_block.py needs.  Rank g owns experts ``[g*E/G, (g+1)*E/G)``; the shared basis, the
+router and the dense shared expert are replicated.  Because the routed experts act in *rank space*,
+what crosses NVLink is small:
+
+  dispatch  one row ``[h_gate | h_up]`` (2r fp16 values) per (token, destination rank) pair -- not per
+            assignment and not the hidden vector -- plus, per assignment, (local expert id, row, weight)
+  combine   one partial ``rank_accum`` row (r_out fp32 values) per (token, destination rank) pair, summed
+            at the token's home rank before the single down-basis product
+
+Both exchanges are ``all_to_all_single`` calls (NCCL over NVLink/NVSwitch on GPUs, gloo in the CPU tests).
+The compute stages are injected, so the same bookkeeping runs against the CUDA library or a CPU oracle.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class DispatchPlan:
+    """Bookkeeping of one dispatch, kept for the combine step."""
+    send_row_token: torch.Tensor      # [rows_sent] home token of every (token, destination) row, grouped by destination
+    send_row_splits: List[int]        # rows sent to each rank
+    recv_row_splits: List[int]        # rows received from each rank
+    recv_assign_splits: List[int]
+
+
+def expert_owner(expert_ids: torch.Tensor, experts_per_rank: int) -> torch.Tensor:
+    return torch.div(expert_ids, experts_per_rank, rounding_mode="floor")
+
+
+def build_dispatch(topk_idx: torch.Tensor, topk_w: torch.Tensor, world: int, experts_per_rank: int):
+    """From the routing of the local tokens: rows and assignments to send, grouped by destination rank.
+
+    Returns (row_token [R], row_splits [G], assign_expert_local [A], assign_row [A], assign_w [A], assign_splits [G]);
+    ``assign_row`` indexes the rows sent to the same destination (0-based inside that destination's block)."""
+    T, k = topk_idx.shape
+    dev = topk_idx.device
+    dest = expert_owner(topk_idx.long(), experts_per_rank)                       # [T, k]
+    pair = torch.zeros((T, world), dtype=torch.bool, device=dev)
+    pair.scatter_(1, dest, True)                                                 # token t talks to rank d
+    pair_t = pair.t().contiguous()                                               # [G, T]
+    row_splits = pair_t.sum(dim=1)
+    row_token = pair_t.nonzero(as_tuple=False)[:, 1]                             # ascending tokens inside every destination
+    # position of token t inside destination d's row block
+    pos_in_block = torch.cumsum(pair_t.to(torch.int64), dim=1) - 1               # [G, T]
+    flat_dest = dest.reshape(-1)
+    flat_tok = torch.arange(T, device=dev).repeat_interleave(k)
+    order = torch.sort(flat_dest, stable=True).indices                           # assignments grouped by destination
+    a_dest = flat_dest[order]
+    a_tok = flat_tok[order]
+    assign_expert_local = (topk_idx.reshape(-1).long()[order] - a_dest * experts_per_rank).to(torch.int32)
+    assign_row = pos_in_block[a_dest, a_tok].to(torch.int32)
+    assign_w = topk_w.reshape(-1)[order].to(torch.float32)
+    assign_splits = torch.bincount(a_dest, minlength=world)
+    return row_token, row_splits, assign_expert_local, assign_row, assign_w, assign_splits
+
+
+def _a2a(t: torch.Tensor, out_splits: List[int], in_splits: List[int], group) -> torch.Tensor:
+    out = t.new_empty((sum(out_splits),) + tuple(t.shape[1:]))
+    dist.all_to_all_single(out, t.contiguous(), out_splits, in_splits, group=group)
+    return out
+
+
+class ExpertParallelLayer:
+    """``experts_fn(h_gate [R,r], h_up [R,r], token_indices [A] int32, expert_offsets [E_local+1] int32,
+    route_w [A] fp32) -> rank_accum [R, r_out] fp32`` is the op contract of ``moe_packed_forward`` applied to
+    the rows this rank received; ``sort_fn(expert_local [A], num_local) -> (order, expert_offsets)`` groups
+    the received assignments by local expert (stable)."""
+
+    def __init__(self, num_experts: int, top_k: int, experts_fn: Callable, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if num_experts % self.world:
+            raise ValueError(f"{num_experts} experts do not shard over {self.world} ranks")
+        self.experts_per_rank = num_experts // self.world
+        self.top_k = top_k
+        self.experts_fn = experts_fn
+
+    def local_expert_range(self) -> Tuple[int, int]:
+        return self.rank * self.experts_per_rank, (self.rank + 1) * self.experts_per_rank
+
+    def forward_rank_space(self, h_gate: torch.Tensor, h_up: torch.Tensor, topk_idx: torch.Tensor,
+                           topk_w: torch.Tensor, rank_out: int) -> torch.Tensor:
+        """h_gate / h_up [T, r] fp16 of the local tokens and their routing -> rank_accum [T, rank_out] fp32."""
+        T, r = h_gate.shape
+        G = self.world
+        row_token, row_splits, a_exp, a_row, a_w, a_splits = build_dispatch(topk_idx, topk_w, G, self.experts_per_rank)
+        # 1. sizes (one small exchange; the only host synchronisation of the layer)
+        sizes = torch.stack((row_splits, a_splits), dim=1).to(torch.int64)           # [G, 2]
+        recv_sizes = torch.empty_like(sizes)
+        dist.all_to_all_single(recv_sizes, sizes, group=self.group)
+        send_rows, send_assign = [int(v) for v in row_splits.tolist()], [int(v) for v in a_splits.tolist()]
+        rs = recv_sizes.tolist()
+        recv_rows, recv_assign = [int(v[0]) for v in rs], [int(v[1]) for v in rs]
+        # 2. dispatch: rank-space rows once per (token, destination), assignment records
+        rows = torch.cat((h_gate.index_select(0, row_token), h_up.index_select(0, row_token)), dim=1)   # [R_send, 2r]
+        rows_in = _a2a(rows, recv_rows, send_rows, self.group)
+        meta = torch.stack((a_exp, a_row), dim=1)
+        meta_in = _a2a(meta, recv_assign, send_assign, self.group)
+        w_in = _a2a(a_w, recv_assign, send_assign, self.group)
+        # rows of source s start at base[s] in the received buffer
+        base = torch.zeros(G, dtype=torch.int64, device=h_gate.device)
+        if G > 1:
+            base[1:] = torch.cumsum(torch.tensor(recv_rows[:-1], device=h_gate.device), 0)
+        src_of_assign = torch.repeat_interleave(torch.arange(G, device=h_gate.device),
+                                                torch.tensor(recv_assign, device=h_gate.device))
+        row_global = meta_in[:, 1].long() + base[src_of_assign]
+        # 3. group the received assignments by local expert (stable) and run the packed experts on them
+        order = torch.sort(meta_in[:, 0].long(), stable=True).indices
+        counts = torch.bincount(meta_in[:, 0].long(), minlength=self.experts_per_rank)
+        offsets = torch.zeros(self.experts_per_rank + 1, dtype=torch.int32, device=h_gate.device)
+        offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        hg_in, hu_in = rows_in[:, :r].contiguous(), rows_in[:, r:].contiguous()
+        if rows_in.shape[0] > 0:
+            partial = self.experts_fn(hg_in, hu_in, row_global[order].to(torch.int32).contiguous(), offsets,
+                                      w_in[order].contiguous())
+        else:
+            partial = torch.zeros((0, rank_out), dtype=torch.float32, device=h_gate.device)
+        # 4. combine: partial rows travel back and are summed at the home rank
+        back = _a2a(partial, send_rows, recv_rows, self.group)                     # same order as `rows`
+        acc = torch.zeros((T, rank_out), dtype=torch.float32, device=h_gate.device)
+        acc.index_add_(0, row_token, back)
+        self.last_plan = DispatchPlan(row_token, send_rows, recv_rows, recv_assign)
+        return acc
+
+
+def shard_tables(tables, rank: int, world: int):
+    """Per-expert buffer lists of a whole layer -> the slice this rank owns."""
+    out = {}
+    for tag, fields in tables.items():
+        n = len(next(iter(fields.values())))
+        per = n // world
+        out[tag] = {f: v[rank * per:(rank + 1) * per] for f, v in fields.items()}
+    return out
+
+
+class ExpertParallelPackedLayer:
+    """GPU layer: this rank's slice of the experts as a ``PackedLayer`` plus the replicated basis; the
+    exchanges run over ``group`` (NCCL)."""
+
+    def __init__(self, tables, vh_gate, vh_up, u_down, intermediate_size: int, rank_out: int, num_experts: int,
+                 top_k: int, norm_topk_prob: bool = True, device=None, group=None):
+        from .layer import PackedLayer
+        self.group = group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        local = shard_tables(tables, rank, world)
+        self.packed = PackedLayer(local["gate"], local["up"], local["down"], intermediate_size, rank_out, vh_gate, vh_up,
+                                  u_down, device=device)
+        self.rank_out = rank_out
+        self.top_k, self.norm_topk_prob = top_k, norm_topk_prob
+        self.ep = ExpertParallelLayer(num_experts, top_k, self.packed.experts_forward, group)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, weight_dtype=torch.float16,
+                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from .layer import route_topk
+        idx, w = route_topk(logits, self.top_k, self.norm_topk_prob, weight_dtype)
+        hg, hu = self.packed.basis_project(x)
+        acc = self.ep.forward_rank_space(hg, hu, idx, w, self.rank_out)
+        return self.packed.combine_down_basis(acc, x.dtype, residual=residual)
