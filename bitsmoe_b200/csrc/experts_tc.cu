@@ -44,9 +44,10 @@ constexpr int XT_BLOCK_BYTES = 128 * 16 * 2;
 constexpr int XT_STAGE_BYTES = XT_STAGE_BLOCKS * XT_BLOCK_BYTES;
 constexpr int XT_CHUNK_STRIDE = XT_NT * 16 + 16;   // bytes between 8-position chunks of the token-side operands (padded: conflict-free stores)
 constexpr int XT_MAX_E = 1024;
+constexpr int XT_SEC = 5;                 // section slots: (tile, matrix) sections up to five ahead
 
 struct XtBars {
-  uint64_t sec_full[3], sec_empty[3];
+  uint64_t sec_full[XT_SEC], sec_empty[XT_SEC];
   uint64_t w_full[XT_RING], w_empty[XT_RING];
   uint64_t act_ready, gu_done, z_ready, tmem_gu_free, down_done;
 };
@@ -90,20 +91,32 @@ __device__ __forceinline__ void dequant_rowpair(const uint32_t* __restrict__ w, 
   for (int p = 0; p < BITS; ++p) words[p] = w[p];
   const uint32_t bias_bits = 0x64006400u + (1u << (BITS - 1)) * 0x00010001u;   // fp16x2 of 1024 + offset
   const __half2 bias = *reinterpret_cast<const __half2*>(&bias_bits);
-  uint32_t lo[8], hi[8];
+  // phase-major so that the eight position chains issue back to back instead of one after the other
+  uint32_t y[8], lo[8], hi[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) y[s] = __funnelshift_r(words[0], words[0], s & 31) & 0x01010101u;
+#pragma unroll
+  for (int p = 1; p < BITS; ++p) {
+#pragma unroll
+    for (int s = 0; s < 8; ++s) y[s] |= __funnelshift_r(words[p], words[p], (s - p) & 31) & (0x01010101u << p);
+  }
 #pragma unroll
   for (int s = 0; s < 8; ++s) {
-    uint32_t y = 0;
+    lo[s] = __byte_perm(y[s], 0x64646464u, 0x4140);   // (1024 + u) for row g,   positions s, s+8
+    hi[s] = __byte_perm(y[s], 0x64646464u, 0x4342);   // (1024 + u) for row g+8, positions s, s+8
+  }
+  __half2 va[8], vb[8];
 #pragma unroll
-    for (int p = 0; p < BITS; ++p) y |= __funnelshift_r(words[p], words[p], (s - p) & 31) & (0x01010101u << p);
-    const uint32_t a = __byte_perm(y, 0x64646464u, 0x4140);   // (1024 + u) for row g,   positions s, s+8
-    const uint32_t b = __byte_perm(y, 0x64646464u, 0x4342);   // (1024 + u) for row g+8, positions s, s+8
-    __half2 va = __hsub2(*reinterpret_cast<const __half2*>(&a), bias);
-    __half2 vb = __hsub2(*reinterpret_cast<const __half2*>(&b), bias);
-    va = __hmul2(va, sc_lo[s]);
-    vb = __hmul2(vb, sc_hi[s]);
-    lo[s] = *reinterpret_cast<uint32_t*>(&va);
-    hi[s] = *reinterpret_cast<uint32_t*>(&vb);
+  for (int s = 0; s < 8; ++s) {
+    va[s] = __hsub2(*reinterpret_cast<const __half2*>(&lo[s]), bias);
+    vb[s] = __hsub2(*reinterpret_cast<const __half2*>(&hi[s]), bias);
+  }
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    va[s] = __hmul2(va[s], sc_lo[s]);
+    vb[s] = __hmul2(vb[s], sc_hi[s]);
+    lo[s] = *reinterpret_cast<uint32_t*>(&va[s]);
+    hi[s] = *reinterpret_cast<uint32_t*>(&vb[s]);
   }
   g_c0 = make_uint4(lo[0], lo[1], lo[2], lo[3]);
   g_c1 = make_uint4(lo[4], lo[5], lo[6], lo[7]);
@@ -124,7 +137,7 @@ struct XtSmem {
   unsigned char* act;     // [2][nchunks][XT_NT rows] canonical K-major, 16-byte chunks
   unsigned char* z;       // [16 chunks][XT_NT rows]
   unsigned char* ring;    // [XT_RING][XT_STAGE_BYTES]
-  unsigned char* sec[3];  // section buffers: [scale (sec_scale_bytes) | words]
+  unsigned char* sec[XT_SEC];  // section buffers: [scale (sec_scale_bytes) | words]
   int* prefix;            // [E + 1] items before each expert
   int16_t* rank_s;        // [2][max_slots] logical rank per slot (gate, up) of the current item's expert
   __half* s_s;            // [2][max_slots]
@@ -138,7 +151,7 @@ __host__ __device__ inline size_t xt_smem_bytes(int max_slots, int max_words, in
   o += static_cast<size_t>(2) * (max_slots / 8) * XT_CHUNK_STRIDE;   // act
   o += static_cast<size_t>(N_TILE / 8) * XT_CHUNK_STRIDE;            // z
   o = align_up_c(o, 128) + static_cast<size_t>(XT_RING) * XT_STAGE_BYTES;       // ring
-  o += 3 * xt_sec_bytes(max_slots, max_words);
+  o += XT_SEC * xt_sec_bytes(max_slots, max_words);
   o += align_up_c(static_cast<size_t>(num_experts + 1) * 4, 128);
   o += align_up_c(static_cast<size_t>(2) * max_slots * 4, 128);
   return o + 1024;                                          // slack for the 1024-byte base alignment
@@ -164,15 +177,15 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
     sm.z = base + o; o += static_cast<size_t>(N_TILE / 8) * XT_CHUNK_STRIDE;
     o = align_up_c(o, 128);
     sm.ring = base + o; o += static_cast<size_t>(XT_RING) * XT_STAGE_BYTES;
-    for (int i = 0; i < 3; ++i) { sm.sec[i] = base + o; o += xt_sec_bytes(max_slots, max_words); }
+    for (int i = 0; i < XT_SEC; ++i) { sm.sec[i] = base + o; o += xt_sec_bytes(max_slots, max_words); }
     sm.prefix = reinterpret_cast<int*>(base + o); o += align_up_c(static_cast<size_t>(num_experts + 1) * 4, 128);
     sm.rank_s = reinterpret_cast<int16_t*>(base + o);
     sm.s_s = reinterpret_cast<__half*>(base + o + static_cast<size_t>(2) * max_slots * 2);
   }
   const size_t sec_scale_bytes = align_up_c(static_cast<size_t>(max_slots) * 2, 128);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 3; ++i) { tc::mbar_init(&bars.sec_full[i], 1); tc::mbar_init(&bars.sec_empty[i], XT_DQ_WARPS); }
-    for (int i = 0; i < XT_RING; ++i) { tc::mbar_init(&bars.w_full[i], XT_DQ_WARPS); tc::mbar_init(&bars.w_empty[i], 1); }
+    for (int i = 0; i < XT_SEC; ++i) { tc::mbar_init(&bars.sec_full[i], 1); tc::mbar_init(&bars.sec_empty[i], XT_DQ_WARPS); }
+    for (int i = 0; i < XT_RING; ++i) { tc::mbar_init(&bars.w_full[i], XT_DQ_WARPS / 2); tc::mbar_init(&bars.w_empty[i], 1); }
     tc::mbar_init(&bars.act_ready, 1);
     tc::mbar_init(&bars.gu_done, 1);
     tc::mbar_init(&bars.z_ready, XT_EPI_WARPS);
@@ -182,14 +195,25 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
     abort_flag_s = 0;
   }
   if (warp == 0) tc::tmem_alloc(&tmem_slot, 512);
-  // items before each expert (an item = up to XT_NT consecutive assignments of one expert)
-  if (threadIdx.x == 32) {
-    int run = 0;
-    for (int e = 0; e < num_experts; ++e) {
-      sm.prefix[e] = run;
-      run += (expert_offsets[e + 1] - expert_offsets[e] + XT_NT - 1) / XT_NT;
+  // items before each expert (an item = up to XT_NT consecutive assignments of one expert): every thread loads
+  // its experts' counts in parallel, one warp then scans them
+  for (int e = threadIdx.x; e < num_experts; e += XT_THREADS)
+    sm.prefix[e + 1] = (expert_offsets[e + 1] - expert_offsets[e] + XT_NT - 1) / XT_NT;
+  __syncthreads();
+  if (warp == 1) {
+    int carry = 0;
+    for (int base = 0; base < num_experts; base += 32) {
+      const int e = base + lane;
+      int v = e < num_experts ? sm.prefix[e + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      if (e < num_experts) sm.prefix[e + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
     }
-    sm.prefix[num_experts] = run;
+    if (lane == 0) sm.prefix[0] = 0;
   }
   tc::fence_before_sync();
   __syncthreads();
@@ -233,6 +257,55 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
     const int nblk_d = fe.m[2].nslots >> 4;
     const int n_mt = (nblk_d + 7) >> 3;   // 128-row tiles of the down product (<= 3)
 
+    // ---- activation operand, once per item, by every warp except the producer and the MMA issuer
+    if (warp != XT_PRODUCER_WARP && warp != XT_MMA_WARP) {
+      constexpr int XT_STAGERS = (XT_EPI_WARPS + XT_DQ_WARPS) * 32;
+      const int tid_s = warp < XT_EPI_WARPS ? threadIdx.x : threadIdx.x - 64;
+      const uint32_t act_m_bytes = static_cast<uint32_t>(max_slots / 8) * XT_CHUNK_STRIDE;
+      // activation operand, once per item: act[m][chunk][n] = 8 consecutive contraction positions of token n
+      for (int m = 0; m < 2; ++m) {
+        const FastMat& fm = fe.m[m];
+        const int16_t* rank_t = reinterpret_cast<const int16_t*>(arena + fm.tab_off);
+        const __half* s_t = reinterpret_cast<const __half*>(arena + fm.tab_off + fm.nslots * 2);
+        for (int i = tid_s; i < fm.nslots; i += XT_STAGERS) {
+          const int rk = rank_t[i];
+          const bool live = rk >= 0 && rk < h_rank;
+          sm.rank_s[m * max_slots + i] = static_cast<int16_t>(live ? rk : 0);
+          sm.s_s[m * max_slots + i] = live ? s_t[i] : __float2half(0.f);
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(XT_STAGERS) : "memory");
+      for (int m = 0; m < 2; ++m) {
+        const FastMat& fm = fe.m[m];
+        const __half* h = m == 0 ? h_gate : h_up;
+        const int16_t* rk_s = sm.rank_s + m * max_slots;
+        const __half* sv_s = sm.s_s + m * max_slots;
+        const int nchunks = fm.nslots >> 3;
+#pragma unroll 2
+        for (int task = tid_s; task < nchunks * XT_NT; task += XT_STAGERS) {
+          const int n = task / nchunks, c8 = task % nchunks;
+          const __half* hrow = h + static_cast<int64_t>(item.tok[n]) * h_rank;
+          const float live = n < n_tok ? 1.f : 0.f;
+          int slot[8];
+          __half hv[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int q = (c8 & 1) * 8 + j;                      // position inside the 16-block
+            slot[j] = (c8 >> 1) * 16 + ((q & 7) >> 1) + 8 * (q & 1) + ((q >> 3) << 2);
+            hv[j] = hrow[rk_s[slot[j]]];
+          }
+          __half v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __float2half_rn(__half2float(hv[j]) * __half2float(sv_s[slot[j]]) * live);
+          *reinterpret_cast<uint4*>(sm.act + m * act_m_bytes + c8 * XT_CHUNK_STRIDE + (n >> 3) * 128 + (n & 7) * 16) =
+              *reinterpret_cast<uint4*>(v);
+        }
+      }
+      tc::fence_async_smem();
+      asm volatile("bar.sync 1, %0;" ::"n"(XT_STAGERS) : "memory");
+      if (tid_s == 0) tc::mbar_arrive(&bars.act_ready);
+
+    }
     if (warp == XT_PRODUCER_WARP) {
       // ------------------------------------------------------------------ producer
       if (lane == 0) {
@@ -240,11 +313,12 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         for (int tile = 0; tile < n_tiles && !*abort_flag; ++tile, ++sr) {
           const unsigned char* unit = arena + fe.unit_base + static_cast<int64_t>(tile) * fe.unit_bytes;
           for (int m = 0; m < 3; ++m) {
-            if (!xt_wait(&bars.sec_empty[m], (sr & 1) ^ 1, abort_flag)) break;
+            const uint32_t use = sr * 3u + m, ss = use % XT_SEC;
+            if (!xt_wait(&bars.sec_empty[ss], ((use / XT_SEC) & 1) ^ 1, abort_flag)) break;
             const uint32_t sb = static_cast<uint32_t>(fe.m[m].nslots) * 2u, wb = static_cast<uint32_t>(fe.m[m].words) * 4u;
-            tc::mbar_expect_tx(&bars.sec_full[m], sb + wb);
-            tc::bulk_g2s(sm.sec[m], unit + fe.sec_off[m], sb, &bars.sec_full[m]);
-            tc::bulk_g2s(sm.sec[m] + sec_scale_bytes, unit + fe.sec_off[3 + m], wb, &bars.sec_full[m]);
+            tc::mbar_expect_tx(&bars.sec_full[ss], sb + wb);
+            tc::bulk_g2s(sm.sec[ss], unit + fe.sec_off[m], sb, &bars.sec_full[ss]);
+            tc::bulk_g2s(sm.sec[ss] + sec_scale_bytes, unit + fe.sec_off[3 + m], wb, &bars.sec_full[ss]);
           }
         }
       }
@@ -306,127 +380,92 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
     else if (warp >= XT_DQ_WARP0) {
       // ------------------------------------------------------------------ dequantisers
       const int dw = warp - XT_DQ_WARP0, tid_d = threadIdx.x - XT_DQ_WARP0 * 32;
-      const uint32_t act_m_bytes = static_cast<uint32_t>(max_slots / 8) * XT_CHUNK_STRIDE;
       XT_TICK_INIT();
-      // activation operand, once per item: act[m][chunk][n] = 8 consecutive contraction positions of token n
-      for (int m = 0; m < 2; ++m) {
-        const FastMat& fm = fe.m[m];
-        const int16_t* rank_t = reinterpret_cast<const int16_t*>(arena + fm.tab_off);
-        const __half* s_t = reinterpret_cast<const __half*>(arena + fm.tab_off + fm.nslots * 2);
-        for (int i = tid_d; i < fm.nslots; i += XT_DQ_WARPS * 32) {
-          const int rk = rank_t[i];
-          const bool live = rk >= 0 && rk < h_rank;
-          sm.rank_s[m * max_slots + i] = static_cast<int16_t>(live ? rk : 0);
-          sm.s_s[m * max_slots + i] = live ? s_t[i] : __float2half(0.f);
-        }
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(XT_DQ_WARPS * 32) : "memory");
-      for (int m = 0; m < 2; ++m) {
-        const FastMat& fm = fe.m[m];
-        const __half* h = m == 0 ? h_gate : h_up;
-        const int16_t* rk_s = sm.rank_s + m * max_slots;
-        const __half* sv_s = sm.s_s + m * max_slots;
-        const int nchunks = fm.nslots >> 3;
-#pragma unroll 2
-        for (int task = tid_d; task < nchunks * XT_NT; task += XT_DQ_WARPS * 32) {
-          const int n = task / nchunks, c8 = task % nchunks;
-          const __half* hrow = h + static_cast<int64_t>(item.tok[n]) * h_rank;
-          const float live = n < n_tok ? 1.f : 0.f;
-          int slot[8];
-          __half hv[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int q = (c8 & 1) * 8 + j;                      // position inside the 16-block
-            slot[j] = (c8 >> 1) * 16 + ((q & 7) >> 1) + 8 * (q & 1) + ((q >> 3) << 2);
-            hv[j] = hrow[rk_s[slot[j]]];
-          }
-          __half v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = __float2half_rn(__half2float(hv[j]) * __half2float(sv_s[slot[j]]) * live);
-          *reinterpret_cast<uint4*>(sm.act + m * act_m_bytes + c8 * XT_CHUNK_STRIDE + (n >> 3) * 128 + (n & 7) * 16) =
-              *reinterpret_cast<uint4*>(v);
-        }
-      }
-      tc::fence_async_smem();
-      asm volatile("bar.sync 1, %0;" ::"n"(XT_DQ_WARPS * 32) : "memory");
-      if (tid_d == 0) tc::mbar_arrive(&bars.act_ready);
-      if (tid_d == 0) XT_TICK(5);
-
-      // warp pair `pair` converts block `pair` of every stage; `unit` = one row pair of that block per thread
-      const int pair = dw >> 1, unit = lane + 32 * (dw & 1), x = unit >> 3, g = unit & 7;
+      // Two teams of four warps take alternate stages; inside a team warp `wt` converts block `wt` of the
+      // stage, two row-pair units per thread (independent chains), so two stages are always in flight.
+      const int team = dw >> 2, wt = dw & 3;
       uint32_t ri = ring_i, sr = sec_round;
       bool ok = true;
       for (int tile = 0; tile < n_tiles && ok; ++tile, ++sr) {
         for (int m = 0; m < 2 && ok; ++m) {
-          ok = xt_wait(&bars.sec_full[m], sr & 1, abort_flag);
+          const uint32_t use = sr * 3u + m, ss = use % XT_SEC;
+          ok = xt_wait(&bars.sec_full[ss], (use / XT_SEC) & 1, abort_flag);
           if (!ok) break;
-          if (tid_d == 0) XT_TICK(6);
           const FastMat& fm = fe.m[m];
-          const uint32_t* words = reinterpret_cast<const uint32_t*>(sm.sec[m] + sec_scale_bytes);
-          const __half2* scale2 = reinterpret_cast<const __half2*>(sm.sec[m]);
+          const uint32_t* words = reinterpret_cast<const uint32_t*>(sm.sec[ss] + sec_scale_bytes);
+          const __half2* scale2 = reinterpret_cast<const __half2*>(sm.sec[ss]);
           const int nkb = fm.nslots >> 4;
           const int e4 = fm.nblk[0], e3 = fm.nblk[0] + fm.nblk[1];
           for (int kb0 = 0; kb0 < nkb; kb0 += XT_STAGE_BLOCKS, ++ri) {
+            if (static_cast<int>(ri & 1u) != team) continue;
             const int slot = ri % XT_RING;
             if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
-            if (tid_d == 0) XT_TICK(7);
-            const int kb = kb0 + pair;
+            const int kb = kb0 + wt;
             if (kb < nkb) {
               int b, boff;
               if (kb < e4) { b = 4; boff = kb * 256; }
               else if (kb < e3) { b = 3; boff = e4 * 256 + (kb - e4) * 192; }
               else { b = 2; boff = e4 * 256 + (e3 - e4) * 192 + (kb - e3) * 128; }
-              const uint32_t* w = words + boff + (x * 8 + g) * b;
               const __half2* sc = scale2 + kb * 8;
-              uint4 c0, c1, d0, d1;
-              if (b == 4) dequant_rowpair<4>(w, sc, sc, c0, c1, d0, d1);
-              else if (b == 3) dequant_rowpair<3>(w, sc, sc, c0, c1, d0, d1);
-              else dequant_rowpair<2>(w, sc, sc, c0, c1, d0, d1);
-              store_unit(sm.ring + slot * XT_STAGE_BYTES + pair * XT_BLOCK_BYTES, x, g, c0, c1, d0, d1);
+              unsigned char* dst = sm.ring + slot * XT_STAGE_BYTES + wt * XT_BLOCK_BYTES;
+              const uint32_t* w0 = words + boff + lane * b;            // unit = lane      -> x = lane >> 3, g = lane & 7
+              const uint32_t* w1 = w0 + 32 * b;                         // unit = lane + 32 -> x + 4
+              uint4 c0, c1, d0, d1, e0, e1, f0, f1;
+              if (b == 4) { dequant_rowpair<4>(w0, sc, sc, c0, c1, d0, d1); dequant_rowpair<4>(w1, sc, sc, e0, e1, f0, f1); }
+              else if (b == 3) { dequant_rowpair<3>(w0, sc, sc, c0, c1, d0, d1); dequant_rowpair<3>(w1, sc, sc, e0, e1, f0, f1); }
+              else { dequant_rowpair<2>(w0, sc, sc, c0, c1, d0, d1); dequant_rowpair<2>(w1, sc, sc, e0, e1, f0, f1); }
+              store_unit(dst, lane >> 3, lane & 7, c0, c1, d0, d1);
+              store_unit(dst, (lane >> 3) + 4, lane & 7, e0, e1, f0, f1);
               tc::fence_async_smem();
             }
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&bars.w_full[slot]);
-            if (tid_d == 0) XT_TICK(8);
           }
           __syncwarp();
-          if (lane == 0) tc::mbar_arrive(&bars.sec_empty[m]);
+          if (lane == 0) tc::mbar_arrive(&bars.sec_empty[ss]);
         }
         if (!ok) break;
-        ok = xt_wait(&bars.sec_full[2], sr & 1, abort_flag);
+        const uint32_t use_d = sr * 3u + 2u, sd = use_d % XT_SEC;
+        ok = xt_wait(&bars.sec_full[sd], (use_d / XT_SEC) & 1, abort_flag);
         if (!ok) break;
         const FastMat& fd = fe.m[2];
-        const uint32_t* dwords = reinterpret_cast<const uint32_t*>(sm.sec[2] + sec_scale_bytes);
-        const __half* scale_d = reinterpret_cast<const __half*>(sm.sec[2]);
+        const uint32_t* dwords = reinterpret_cast<const uint32_t*>(sm.sec[sd] + sec_scale_bytes);
+        const __half* scale_d = reinterpret_cast<const __half*>(sm.sec[sd]);
         for (int mt = 0; mt < n_mt && ok; ++mt) {
-          const int mb = 8 * mt + x;
-          int b = 0, boff = 0;
-          if (mb < nblk_d) {
-            if (mb < fd.nblk[0]) { b = 4; boff = mb * 256; }
-            else if (mb < fd.nblk[0] + fd.nblk[1]) { b = 3; boff = fd.nblk[0] * 256 + (mb - fd.nblk[0]) * 192; }
-            else { b = 2; boff = fd.nblk[0] * 256 + fd.nblk[1] * 192 + (mb - fd.nblk[0] - fd.nblk[1]) * 128; }
-          }
-          __half2 sg[8], sh[8];
-          if (b) {
-            const __half a = scale_d[16 * mb + g], c = scale_d[16 * mb + g + 8];
+          // this thread's two units: row-pair g of slot blocks 8*mt + x and 8*mt + x + 4
+          int bb[2], bo[2];
+          __half2 sg[2], sh[2];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { sg[i] = __halves2half2(a, a); sh[i] = __halves2half2(c, c); }
+          for (int u = 0; u < 2; ++u) {
+            const int mb = 8 * mt + (lane >> 3) + 4 * u, g = lane & 7;
+            bb[u] = 0; bo[u] = 0;
+            sg[u] = sh[u] = __float2half2_rn(0.f);
+            if (mb < nblk_d) {
+              if (mb < fd.nblk[0]) { bb[u] = 4; bo[u] = mb * 256; }
+              else if (mb < fd.nblk[0] + fd.nblk[1]) { bb[u] = 3; bo[u] = fd.nblk[0] * 256 + (mb - fd.nblk[0]) * 192; }
+              else { bb[u] = 2; bo[u] = fd.nblk[0] * 256 + fd.nblk[1] * 192 + (mb - fd.nblk[0] - fd.nblk[1]) * 128; }
+              sg[u] = __half2half2(scale_d[16 * mb + g]);
+              sh[u] = __half2half2(scale_d[16 * mb + g + 8]);
+            }
           }
           for (int kb0 = 0; kb0 < 8; kb0 += XT_STAGE_BLOCKS, ++ri) {
+            if (static_cast<int>(ri & 1u) != team) continue;
             const int slot = ri % XT_RING;
             if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
-            const int kb = kb0 + pair;
-            unsigned char* dst = sm.ring + slot * XT_STAGE_BYTES + pair * XT_BLOCK_BYTES;
-            if (b) {
-              const uint32_t* w = dwords + boff + (kb * 8 + g) * b;
-              uint4 c0, c1, d0, d1;
-              if (b == 4) dequant_rowpair<4>(w, sg, sh, c0, c1, d0, d1);
-              else if (b == 3) dequant_rowpair<3>(w, sg, sh, c0, c1, d0, d1);
-              else dequant_rowpair<2>(w, sg, sh, c0, c1, d0, d1);
-              store_unit(dst, x, g, c0, c1, d0, d1);
-            } else {
-              const uint4 zero = make_uint4(0, 0, 0, 0);
-              store_unit(dst, x, g, zero, zero, zero, zero);
+            const int kb = kb0 + wt, g = lane & 7;
+            unsigned char* dst = sm.ring + slot * XT_STAGE_BYTES + wt * XT_BLOCK_BYTES;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0, d0 = c0, d1 = c0;
+              if (bb[u]) {
+                const uint32_t* w = dwords + bo[u] + (kb * 8 + g) * bb[u];
+                const __half2 sgl[8] = {sg[u], sg[u], sg[u], sg[u], sg[u], sg[u], sg[u], sg[u]};
+                const __half2 shl[8] = {sh[u], sh[u], sh[u], sh[u], sh[u], sh[u], sh[u], sh[u]};
+                if (bb[u] == 4) dequant_rowpair<4>(w, sgl, shl, c0, c1, d0, d1);
+                else if (bb[u] == 3) dequant_rowpair<3>(w, sgl, shl, c0, c1, d0, d1);
+                else dequant_rowpair<2>(w, sgl, shl, c0, c1, d0, d1);
+              }
+              store_unit(dst, (lane >> 3) + 4 * u, g, c0, c1, d0, d1);
             }
             tc::fence_async_smem();
             __syncwarp();
@@ -434,7 +473,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
           }
         }
         __syncwarp();
-        if (ok && lane == 0) tc::mbar_arrive(&bars.sec_empty[2]);
+        if (ok && lane == 0) tc::mbar_arrive(&bars.sec_empty[sd]);
       }
     } else {
       // ------------------------------------------------------------------ epilogue warps 0-3

@@ -321,11 +321,23 @@ extern "C" int bm_layer_create(const bm_layer_desc_t* desc, void* arena, size_t 
     if (rc) { delete L; return rc; }
     L->fast_ok = true;
   }
+  // host-side objects for the fork/join of routing and basis projection (no device memory)
+  if (cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&L->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&L->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+    L->side_stream = nullptr;
+    (void)cudaGetLastError();
+  }
   *out = L;
   return BM_OK;
 }
 
 extern "C" int bm_layer_destroy(bm_layer_t* layer) {
+  if (layer) {
+    if (layer->ev_fork) cudaEventDestroy(layer->ev_fork);
+    if (layer->ev_join) cudaEventDestroy(layer->ev_join);
+    if (layer->side_stream) cudaStreamDestroy(layer->side_stream);
+  }
   delete layer;
   return BM_OK;
 }
@@ -498,12 +510,27 @@ extern "C" int bm_layer_forward(const bm_layer_t* L, const void* x, int x_dtype,
   BM_REQUIRE(workspace && workspace_bytes >= w.total && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
              BM_ERR_WORKSPACE, "layer_forward: workspace must be 256-byte aligned and hold %zu bytes (%zu given)", w.total,
              workspace_bytes);
+  // routing depends only on the logits and the basis projection only on x: run them side by side
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool fork = L->side_stream != nullptr && L->ev_fork != nullptr && L->ev_join != nullptr;
+  void* route_stream = stream;
+  if (fork) {
+    BM_CUDA(cudaEventRecord(L->ev_fork, st));
+    BM_CUDA(cudaStreamWaitEvent(L->side_stream, L->ev_fork, 0));
+    route_stream = L->side_stream;
+  }
   int rc = bm_route(logits, logits_dtype, T, num_routed, k, renorm, weight_round, global_to_local, L->num_experts, TILE_ROWS,
                     w.topk_idx, w.topk_w, w.token_indices, w.expert_offsets, w.route_flat, w.tile_table, w.counts, w.route_ws,
-                    w.route_ws_bytes, stream);
+                    w.route_ws_bytes, route_stream);
+  const int rc_basis =
+      bm_basis_project(L, x, x_dtype, T, reinterpret_cast<uint16_t*>(w.h_gate), reinterpret_cast<uint16_t*>(w.h_up), stream);
+  if (fork) {
+    // always join, also on error, so that the side stream never stays attached to a capture
+    cudaEventRecord(L->ev_join, L->side_stream);
+    cudaStreamWaitEvent(st, L->ev_join, 0);
+  }
   if (rc) return rc;
-  rc = bm_basis_project(L, x, x_dtype, T, reinterpret_cast<uint16_t*>(w.h_gate), reinterpret_cast<uint16_t*>(w.h_up), stream);
-  if (rc) return rc;
+  if (rc_basis) return rc_basis;
   // Dropped assignments (experts that are not packed) leave a shorter list; the kernels walk
   // expert_offsets, so passing the upper bound T*k as num_assign is safe.
   rc = bm_experts_forward(L, reinterpret_cast<const uint16_t*>(w.h_gate), reinterpret_cast<const uint16_t*>(w.h_up),

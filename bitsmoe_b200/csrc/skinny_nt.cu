@@ -51,13 +51,14 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_nt_kernel(SkinnyArgs a) {
   const __half* W = a.W[wsel] + static_cast<size_t>(mloc0) * a.K + static_cast<size_t>(split) * ks;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
-  // W slice -> smem, 16-byte vectors
+  // W slice -> smem with cp.async (16-byte vectors), so it streams in while the token rows are converted
   const int vec_per_row = ks / 8;
   for (int v = threadIdx.x; v < a.mrows * vec_per_row; v += SK_THREADS) {
     const int r = v / vec_per_row, c = (v - r * vec_per_row) * 8;
-    const uint4 val = *reinterpret_cast<const uint4*>(W + static_cast<size_t>(r) * a.K + c);
-    *reinterpret_cast<uint4*>(Ws + static_cast<size_t>(r) * stride + c) = val;
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(Ws + static_cast<size_t>(r) * stride + c));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(W + static_cast<size_t>(r) * a.K + c) : "memory");
   }
+  asm volatile("cp.async.commit_group;" ::: "memory");
   const int mblocks = a.mrows / 16;
   for (int n0 = 0; n0 < a.N; n0 += SK_NTOK) {
     const int nn = min(SK_NTOK, a.N - n0);
@@ -91,6 +92,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_nt_kernel(SkinnyArgs a) {
       }
       *reinterpret_cast<uint4*>(Xs + static_cast<size_t>(r) * stride + c) = *reinterpret_cast<uint4*>(out);
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     // (mblock, nblock) items round-robin over the warps
     for (int item = warp; item < mblocks * nblocks; item += SK_THREADS / 32) {
