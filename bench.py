@@ -249,7 +249,7 @@ def gpu_arm(args):
         for i in range(max(warmup, 3)):
             step(i)
         barrier()
-        ms = timed(step, steps, sync, use_graph=(world == 1))
+        ms = timed(step, steps, sync, use_graph=True)
         out = {"tokens": T, "ms_per_step": ms / steps, "tokens_per_s": T * steps / (ms * 1e-3)}
         if want_roofline and world > 1:
             out.update(experts_kernel_ms=None, experts_bytes=None, active_experts=None)
@@ -293,7 +293,7 @@ def gpu_arm(args):
         for i in range(max(warmup, 3)):
             step(i)
         barrier()
-        ms = timed(step, steps, sync, use_graph=(world == 1))
+        ms = timed(step, steps, sync, use_graph=True)
         return {"value": T * steps / (ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": dx.numel() * 2 + dl.numel() * 4,
                 "d2h_bytes_per_step": dy.numel() * 2}
 
@@ -348,7 +348,7 @@ def gpu_arm(args):
                    "l2": f"inputs larger than L2: {L} distinct weight sets of ~23 MB rotate through the timed loop",
                    "launch": "all timed steps captured in one CUDA graph, replayed once inside the CUDA-event bracket",
                    "parallelism": "1 GPU" if world == 1 else
-                   f"ep{world}: experts sharded over {world} GPUs, rank-space all-to-all dispatch/combine (NCCL), eager launches"},
+                   f"ep{world}: experts sharded over {world} GPUs, rank-space all_gather dispatch / reduce_scatter combine (NCCL), captured in the same CUDA graph"},
         "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": (achieved / pk["hbm_gbs"]) if achieved else None, "traffic": None, "peak_source": pk["source"],

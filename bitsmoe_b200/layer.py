@@ -145,11 +145,13 @@ class PackedLayer:
     def route_topk(self, logits: torch.Tensor, top_k: int, norm_topk_prob: bool, weight_dtype) -> Tuple[torch.Tensor, torch.Tensor]:
         return route_topk(logits, top_k, norm_topk_prob, weight_dtype)
 
-    def basis_project(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    def basis_project(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """h_gate, h_up [T, r] fp16; ``out`` may be a preallocated [2, T, r] fp16 tensor that receives both."""
         x = x.contiguous()
         T = x.shape[0]
-        hg = torch.empty((T, self.rank_in), dtype=torch.float16, device=self.device)
-        hu = torch.empty_like(hg)
+        if out is None:
+            out = torch.empty((2, T, self.rank_in), dtype=torch.float16, device=self.device)
+        hg, hu = out[0], out[1]
         with torch.cuda.device(self.device):
             capi.check(capi.lib().bm_basis_project(self._handle, x.data_ptr(), capi.dtype_code(x.dtype), T,
                                                    hg.data_ptr(), hu.data_ptr(), capi.stream_ptr(self.device)))

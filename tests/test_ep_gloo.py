@@ -75,3 +75,44 @@ def test_dispatch_plan_dedups_token_destination_pairs():
     assert a_splits.tolist() == [5, 4]
     assert a_exp.tolist() == [0, 1, 2, 3, 0, 1, 0, 2, 3]
     assert a_row.tolist() == [0, 0, 1, 1, 1, 0, 1, 1, 1]
+
+
+def _gather_worker(rank: int, world: int, port: int, T: int, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        cfg = synth.tiny(hidden=128, num_experts=8, intermediate=128, top_k=3, rank=32)
+        layer = synth.make_layer(cfg, seed=21)
+        experts = helpers.decoded_experts(layer)
+        per = cfg.num_experts // world
+        local = experts[rank * per:(rank + 1) * per]
+
+        def route_build_fn(idx, w, g2l):
+            return oforward.build_routing(idx.long(), w, per, g2l)
+
+        def experts_fn(hg, hu, tok, off, rw):
+            n = hu.shape[0]                                   # the up view is T rows shorter
+            return oforward.packed_forward(hg[:n], hu, tok, off, rw, local, cfg.rank)
+
+        x = synth.activations(cfg, T, seed=100 + rank)
+        logits = synth.router_logits(cfg, T, seed=200 + rank, zipf_s=0.8)
+        idx, w = oforward.router(logits, cfg.top_k, True, torch.float16)
+        hg, hu = oforward.basis_project(x, layer.vh_gate), oforward.basis_project(x, layer.vh_up)
+        gep = ep.GatherExpertParallel(cfg.num_experts, cfg.top_k, route_build_fn, experts_fn)
+        acc = gep.forward_rank_space(torch.stack((hg, hu)), idx.to(torch.int32), w, cfg.rank)
+        tok, off, rw = oforward.build_routing(idx, w, cfg.num_experts)
+        want = oforward.packed_forward(hg, hu, tok, off, rw, experts, cfg.rank)
+        ret[rank] = float((acc - want).abs().max())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gather_expert_parallel_matches_single_rank(world):
+    ret = mp.Manager().dict()
+    mp.spawn(_gather_worker, args=(world, _free_port(), 9, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for rank in range(world):
+        assert ret[rank] < 1e-5, (rank, ret[rank])

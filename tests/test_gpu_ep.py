@@ -28,13 +28,17 @@ def _worker(rank, world, port, ret):
         full = synth.to_packed_layer(layer, dev)
         epl = ep.ExpertParallelPackedLayer(layer.tables, layer.vh_gate, layer.vh_up, layer.u_down, cfg.intermediate,
                                            cfg.rank, cfg.num_experts, cfg.top_k, device=dev)
-        T = 40 + 8 * rank
-        x = synth.activations(cfg, T, seed=300 + rank, device=dev)
-        logits = synth.router_logits(cfg, T, seed=400 + rank, device=dev)
-        y_ep = epl.forward(x, logits, torch.bfloat16)
-        y_one = full.forward(x, logits, cfg.top_k, True, torch.bfloat16)
-        torch.cuda.synchronize()
-        ret[rank] = float((y_ep.float() - y_one.float()).abs().max()), float(y_one.float().abs().max())
+        worst, mag = 0.0, 0.0
+        # 48 tokens everywhere: gathered fixed-size exchange; 300 + 8*rank tokens: ragged all-to-all exchange
+        for T in (48, 300 + 8 * rank):
+            x = synth.activations(cfg, T, seed=300 + rank, device=dev)
+            logits = synth.router_logits(cfg, T, seed=400 + rank, device=dev)
+            y_ep = epl.forward(x, logits, torch.bfloat16)
+            y_one = full.forward(x, logits, cfg.top_k, True, torch.bfloat16)
+            torch.cuda.synchronize()
+            worst = max(worst, float((y_ep.float() - y_one.float()).abs().max()))
+            mag = max(mag, float(y_one.float().abs().max()))
+        ret[rank] = worst, mag
     finally:
         dist.destroy_process_group()
 
