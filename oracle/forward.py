@@ -100,10 +100,11 @@ def packed_forward(h_gate: torch.Tensor, h_up: torch.Tensor, token_indices: torc
     out = torch.zeros((T, rank_out), dtype=acc_t)
     hg, hu = h_gate.to(torch.float32), h_up.to(torch.float32)
     off = expert_offsets.tolist()
-    for e, ex in enumerate(experts):
+    for e in range(len(experts)):
         a0, a1 = off[e], off[e + 1]
         if a1 <= a0:
             continue
+        ex = experts[e]
         tok = token_indices[a0:a1].long()
         rw = route_weights[a0:a1].to(torch.float32)
 

@@ -95,3 +95,23 @@ def assert_close(got: torch.Tensor, want: torch.Tensor, rtol: float = RTOL, atol
     bad = err > bound
     assert not bool(bad.any()), (f"{what}: {int(bad.sum())}/{bad.numel()} outside rtol={rtol} atol={atol}; "
                                  f"max abs err {float(err.max()):.4g}, max |want| {float(want.abs().max()):.4g}")
+
+
+class LazyDecodedExperts:
+    """Sequence of DecodedExpert that dequantises an expert only when the oracle touches it (large layers)."""
+
+    def __init__(self, layer: synth.SynthLayer):
+        self.layer, self._cache = layer, {}
+
+    def __len__(self):
+        return self.layer.cfg.num_experts
+
+    def __getitem__(self, e):
+        if e not in self._cache:
+            I = self.layer.cfg.intermediate
+            self._cache[e] = oforward.DecodedExpert(table_entry(self.layer, "gate", e), table_entry(self.layer, "up", e),
+                                                    table_entry(self.layer, "down", e), I)
+        return self._cache[e]
+
+    def __iter__(self):
+        return (self[e] for e in range(len(self)))
