@@ -59,7 +59,7 @@ struct XtItem {
   int n, expert;
 };
 
-__device__ __forceinline__ bool xt_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool xt_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t backoff_ns = 0) {
   const uint32_t addr = tc::smem_u32(bar);
   uint64_t t0 = 0;
   for (uint32_t i = 0;; ++i) {
@@ -71,6 +71,7 @@ __device__ __forceinline__ bool xt_wait(uint64_t* bar, uint32_t parity, volatile
         : "memory");
     if (done) return true;
     if (*abort_flag) return false;
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((i & 15u) == 15u) {
       const uint64_t now = tc::global_ns();
       if (t0 == 0) t0 = now;
@@ -486,8 +487,8 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
       const int c_pos = (c & ~15) + kperm16(c & 15);
       unsigned char* zrow = sm.z + (c_pos >> 3) * XT_CHUNK_STRIDE + (c_pos & 7) * 2;
       for (int tile = 0; tile < n_tiles && ok; ++tile, ++gr) {
-        ok = xt_wait(&bars.gu_done, gr & 1, abort_flag);
-        if (ok && gr > 0) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag);
+        ok = xt_wait(&bars.gu_done, gr & 1, abort_flag, 200);
+        if (ok && gr > 0) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag, 200);
         if (!ok) break;
         if (threadIdx.x == 0) XT_TICK(9);
         tc::fence_after_sync();
@@ -509,7 +510,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         if (lane == 0) { tc::mbar_arrive(&bars.tmem_gu_free); tc::mbar_arrive(&bars.z_ready); }
         if (threadIdx.x == 0) XT_TICK(10);
       }
-      if (ok) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag);
+      if (ok) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag, 200);
       if (threadIdx.x == 0) XT_TICK(11);
       if (ok) {
         tc::fence_after_sync();
