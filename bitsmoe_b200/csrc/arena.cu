@@ -23,25 +23,26 @@ void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P) {
       const MatHost& mh = L->host[w][e];
       if (mh.n_rows > 32000) return;
       FastMat& fm = P->experts[e].m[w];
-      std::vector<int16_t> rows[3];
+      std::vector<int16_t> rows[2];
       for (const SlabHost& s : mh.slabs) {
-        if (s.bits < 2 || s.bits > 4) return;
+        if (s.bits < 1 || s.bits > 4) return;
         if (s.tile_end - s.tile_off != L->n_tiles) return;
-        for (int r = 0; r < s.k_slab; ++r) rows[4 - s.bits].push_back(static_cast<int16_t>(s.rank_off + r));
+        for (int r = 0; r < s.k_slab; ++r) rows[s.bits >= 3 ? 0 : 1].push_back(static_cast<int16_t>(s.rank_off + r));
       }
       P->slot_row_off[e * 3 + w] = static_cast<int32_t>(P->slot_row.size());
-      int total_blk = 0, words = 0;
-      for (int g = 0; g < 3; ++g) {
-        const int nb = (static_cast<int>(rows[g].size()) + 15) / 16;
-        fm.nblk[g] = nb;
-        total_blk += nb;
-        words += 64 * group_bits(g) * nb;
-        for (int i = 0; i < nb * 16; ++i)
+      // gate / up contract over the slots in pairs of 16-blocks; down only needs whole 16-row blocks
+      const int gran = w < 2 ? 32 : 16;
+      int total_blk = 0;
+      for (int g = 0; g < 2; ++g) {
+        const int padded = (static_cast<int>(rows[g].size()) + gran - 1) / gran * gran;
+        fm.nblk[g] = padded / 16;
+        total_blk += fm.nblk[g];
+        for (int i = 0; i < padded; ++i)
           P->slot_row.push_back(i < static_cast<int>(rows[g].size()) ? rows[g][i] : static_cast<int16_t>(-1));
       }
       if (total_blk == 0) return;
       fm.nslots = total_blk * 16;
-      fm.words = words;
+      fm.words = 256 * fm.nblk[0] + 128 * fm.nblk[1];
       fm.tab_off = static_cast<int32_t>(off);
       off += align_up(static_cast<size_t>(fm.nslots) * 6, 16);
       if (fm.nslots > P->max_slots) P->max_slots = fm.nslots;
@@ -55,7 +56,7 @@ void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P) {
     FastExpert& fe = P->experts[e];
     int o = 0;
     for (int w = 0; w < 3; ++w) { fe.sec_off[w] = o; o += fe.m[w].nslots * 2; }       // multiples of 32 bytes
-    for (int w = 0; w < 3; ++w) { fe.sec_off[3 + w] = o; o += fe.m[w].words * 4; }   // multiples of 256 bytes
+    for (int w = 0; w < 3; ++w) { fe.sec_off[3 + w] = o; o += fe.m[w].words * 4; }   // multiples of 512 bytes
     fe.unit_bytes = static_cast<int32_t>(align_up(o, 128));
     fe.unit_base = static_cast<int64_t>(off);
     off += static_cast<size_t>(fe.unit_bytes) * L->n_tiles;
@@ -67,38 +68,21 @@ void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P) {
               2 * FAST_MAX_TOK * (P->max_slots + 8) * 2 + 8192 <= 200 * 1024 && L->rank_in % 8 == 0;
 }
 
-__device__ __forceinline__ int source_bit(const MatDev& md, int row, int col_in_tile, int tile, int plane, int* bits_out) {
-  // bit `plane` of u(row, tile*128 + col_in_tile) read from the reference payload
+// signed code q(row, tile*128 + col_in_tile) read from the reference payload
+__device__ __forceinline__ int source_q(const MatDev& md, int row, int col_in_tile, int tile) {
   for (int sl = 0; sl < md.n_slabs; ++sl) {
     const int k_slab = md.slab_meta[sl * 4 + 1], rank_off = md.slab_meta[sl * 4 + 2];
     if (row < rank_off || row >= rank_off + k_slab) continue;
     const int bits = md.slab_meta[sl * 4 + 0];
-    *bits_out = bits;
-    if (plane >= bits) return 0;
     const int t = md.slab_meta[sl * 4 + 3] + tile;
     const int r = row - rank_off, s0 = (r / K_STAGE) * K_STAGE, rows_cur = min(K_STAGE, k_slab - s0);
-    const uint32_t w = md.payload[md.tile_meta[t * 3 + 0] + s0 * MICROS * bits + (col_in_tile / N_MICRO) * rows_cur * bits +
-                                  (r - s0) * bits + plane];
-    return static_cast<int>((w >> (col_in_tile % N_MICRO)) & 1u);
+    const uint32_t* w = md.payload + md.tile_meta[t * 3 + 0] + s0 * MICROS * bits + (col_in_tile / N_MICRO) * rows_cur * bits +
+                        (r - s0) * bits;
+    int u = 0;
+    for (int p = 0; p < bits; ++p) u |= static_cast<int>((w[p] >> (col_in_tile % N_MICRO)) & 1u) << p;
+    return bits == 1 ? 2 * u - 1 : u - (1 << (bits - 1));
   }
-  *bits_out = 0;
   return 0;
-}
-
-__device__ __forceinline__ void slot_group(const FastMat& fm, int blk, int* grp, int* blk_in_grp) {
-  if (blk < fm.nblk[0]) { *grp = 0; *blk_in_grp = blk; }
-  else if (blk < fm.nblk[0] + fm.nblk[1]) { *grp = 1; *blk_in_grp = blk - fm.nblk[0]; }
-  else { *grp = 2; *blk_in_grp = blk - fm.nblk[0] - fm.nblk[1]; }
-}
-
-// word offset of slot-block `blk` inside a matrix section (both orientations store 64*b words per block)
-__device__ __forceinline__ int block_word_off(const FastMat& fm, int blk) {
-  int grp, big;
-  slot_group(fm, blk, &grp, &big);
-  int off = 0;
-  if (grp >= 1) off += fm.nblk[0] * 64 * 4;
-  if (grp >= 2) off += fm.nblk[1] * 64 * 3;
-  return off + big * 64 * group_bits(grp);
 }
 
 // grid (E, n_tiles, 3): fills rank / s / row tables (tile 0 only) and this tile's scales.
@@ -128,8 +112,8 @@ __global__ void __launch_bounds__(128) repack_tables_kernel(const ExpertDev* __r
         break;
       }
     }
-    // gate / up scales are stored in the contraction order of the MMA operands (pairs (s, s+8) adjacent)
-    scale_out[w < 2 ? (slot & ~15) + kperm16(slot & 15) : slot] = sc;
+    // gate / up scales are stored in the order of the token-side operand (see pos32)
+    scale_out[w < 2 ? slot_pos(slot) : slot] = sc;
     if (tile == 0) {
       int rk = row >= 0 ? md.rank_idx[row] : -1;
       if (rk < 0 || rk > 32000) rk = -1;
@@ -138,6 +122,31 @@ __global__ void __launch_bounds__(128) repack_tables_kernel(const ExpertDev* __r
       t_row[slot] = static_cast<int16_t>(row);
     }
   }
+}
+
+// Where the codes of word `i` of a matrix section come from.  `first_blk` = the word's first 16-slot (gate/up:
+// contraction, down: operand-row) block, `x` = the block of 16 along the tile's columns, `nb` = blocks per word.
+struct WordGeom {
+  int dense, slot_blk, col_blk, lane, nb;
+};
+__device__ __forceinline__ WordGeom word_geom(const FastMat& fm, int w, int i) {
+  WordGeom q;
+  const int nib_words = fm.nblk[0] * 256;
+  q.dense = i >= nib_words;
+  if (!q.dense) {
+    q.nb = 1;
+    q.lane = (i >> 1) & 31;
+    const int blk = i & 1;
+    if (w < 2) { q.slot_blk = (i >> 9) * 2 + blk; q.col_blk = (i >> 6) & 7; }
+    else { q.slot_blk = i >> 8; q.col_blk = ((i >> 6) & 3) * 2 + blk; }
+  } else {
+    const int j = i - nib_words;
+    q.nb = 2;
+    q.lane = j & 31;
+    if (w < 2) { q.slot_blk = fm.nblk[0] + (j >> 8) * 2; q.col_blk = (j >> 5) & 7; }
+    else { q.slot_blk = fm.nblk[0] + (j >> 7); q.col_blk = ((j >> 5) & 3) * 2; }
+  }
+  return q;
 }
 
 // grid (E, n_tiles, 3): one thread per output word.
@@ -152,35 +161,23 @@ __global__ void __launch_bounds__(256) repack_words_kernel(const ExpertDev* __re
   const FastMat& fm = fe.m[w];
   const int16_t* slot_row = slot_row_all + slot_row_off[e * 3 + w];
   uint32_t* out = reinterpret_cast<uint32_t*>(arena + fe.unit_base + static_cast<int64_t>(tile) * fe.unit_bytes + fe.sec_off[3 + w]);
-  const int nblk = fm.nslots / 16;
-  for (int blk = 0; blk < nblk; ++blk) {
-    int grp, big;
-    slot_group(fm, blk, &grp, &big);
-    const int b = group_bits(grp);
-    const int base = block_word_off(fm, blk);
-    // 64*b words of this slot block: index = ((x * 8) + g) * b + plane, x = the other dimension's block (0..7)
-    for (int i = threadIdx.x; i < 64 * b; i += blockDim.x) {
-      const int plane = i % b, g = (i / b) % 8, x = i / (8 * b);
-      uint32_t word = 0;
-      int dummy;
-      if (w < 2) {
-        // gate / up: operand rows are columns c = 16*x + g (+8); contraction = slots of this block
-        for (int k = 0; k < 16; ++k) {
-          const int row = slot_row[blk * 16 + k];
-          if (row < 0) continue;
-          word |= static_cast<uint32_t>(source_bit(md, row, 16 * x + g, tile, plane, &dummy)) << k;
-          word |= static_cast<uint32_t>(source_bit(md, row, 16 * x + g + 8, tile, plane, &dummy)) << (16 + k);
+  for (int i = threadIdx.x; i < fm.words; i += blockDim.x) {
+    const WordGeom q = word_geom(fm, w, i);
+    const int g = q.lane >> 2, t = q.lane & 3;
+    uint32_t word = 0;
+    for (int blk = 0; blk < q.nb; ++blk)
+      for (int hi8 = 0; hi8 < 2; ++hi8)
+        for (int kk = 0; kk < 4; ++kk) {
+          const int k = 2 * t + (kk & 1) + 8 * (kk >> 1);
+          int slot, col;
+          if (w < 2) { slot = (q.slot_blk + blk) * 16 + k; col = q.col_blk * 16 + g + 8 * hi8; }     // contraction = slots
+          else { slot = q.slot_blk * 16 + g + 8 * hi8; col = (q.col_blk + blk) * 16 + k; }           // contraction = columns
+          const int row = slot_row[slot];
+          const int code = row >= 0 ? source_q(md, row, col, tile) : 0;
+          if (q.dense) word |= static_cast<uint32_t>((code + FAST_DENSE_OFFSET) & 3) << dense_shift(blk, hi8, k);
+          else word |= static_cast<uint32_t>((code + FAST_NIB_OFFSET) & 15) << nib_shift(hi8, k);
         }
-      } else {
-        // down: operand rows are slots g, g+8 of this block; contraction = columns 16*x .. 16*x+15
-        const int r0 = slot_row[blk * 16 + g], r1 = slot_row[blk * 16 + g + 8];
-        for (int k = 0; k < 16; ++k) {
-          if (r0 >= 0) word |= static_cast<uint32_t>(source_bit(md, r0, 16 * x + k, tile, plane, &dummy)) << k;
-          if (r1 >= 0) word |= static_cast<uint32_t>(source_bit(md, r1, 16 * x + k, tile, plane, &dummy)) << (16 + k);
-        }
-      }
-      out[base + i] = word;
-    }
+    out[i] = word;
   }
 }
 
@@ -199,27 +196,24 @@ __global__ void __launch_bounds__(256) arena_decode_kernel(const FastExpert* __r
     if (row < 0) continue;
     const int tile = col / N_TILE, cc = col % N_TILE;
     const uint32_t* words = reinterpret_cast<const uint32_t*>(arena + fe.unit_base + static_cast<int64_t>(tile) * fe.unit_bytes + fe.sec_off[3 + w]);
-    const int blk = slot / 16, k = slot % 16;
-    int grp, big;
-    slot_group(fm, blk, &grp, &big);
-    const int b = group_bits(grp);
-    const uint32_t* wb = words + block_word_off(fm, blk);
-    int u = 0;
-    for (int p = 0; p < b; ++p) {
-      uint32_t word;
-      int bitpos;
-      if (w < 2) {
-        const int x = cc / 16, r = cc % 16;
-        word = wb[((x * 8) + (r & 7)) * b + p];
-        bitpos = (r >= 8 ? 16 : 0) + k;
-      } else {
-        const int x = cc / 16;
-        word = wb[((x * 8) + (k & 7)) * b + p];
-        bitpos = (k >= 8 ? 16 : 0) + (cc % 16);
-      }
-      u |= static_cast<int>((word >> bitpos) & 1u) << p;
+    const int sblk = slot >> 4, cblk = cc >> 4;
+    // operand row / contraction index inside the 16x16 block
+    const int m = w < 2 ? (cc & 15) : (slot & 15), k = w < 2 ? (slot & 15) : (cc & 15);
+    const int lane = (m & 7) * 4 + ((k & 7) >> 1), hi8 = m >> 3;
+    int q;
+    if (sblk < fm.nblk[0]) {
+      int idx;
+      if (w < 2) idx = (((sblk >> 1) * 8 + cblk) * 32 + lane) * 2 + (sblk & 1);
+      else idx = ((sblk * 4 + (cblk >> 1)) * 32 + lane) * 2 + (cblk & 1);
+      q = static_cast<int>((words[idx] >> nib_shift(hi8, k)) & 15u) - FAST_NIB_OFFSET;
+    } else {
+      const int db = sblk - fm.nblk[0];
+      int idx, blk;
+      if (w < 2) { idx = ((db >> 1) * 8 + cblk) * 32 + lane; blk = db & 1; }
+      else { idx = (db * 4 + (cblk >> 1)) * 32 + lane; blk = cblk & 1; }
+      q = static_cast<int>((words[fm.nblk[0] * 256 + idx] >> dense_shift(blk, hi8, k)) & 3u) - FAST_DENSE_OFFSET;
     }
-    codes[static_cast<int64_t>(row) * intermediate + col] = static_cast<int8_t>(u - (1 << (b - 1)));
+    codes[static_cast<int64_t>(row) * intermediate + col] = static_cast<int8_t>(q);
   }
 }
 

@@ -74,11 +74,11 @@ struct MatHost {
 constexpr int FAST_MAX_TOK = 8;    // assignments per pass of the decode kernel (one MMA N-block)
 
 struct FastMat {
-  int32_t nblk[3];      // 16-slot blocks holding 4-, 3-, 2-bit rows
-  int32_t nslots;       // 16 * total blocks
-  int32_t words;        // uint32 words per tile = 64 * (4 nblk[0] + 3 nblk[1] + 2 nblk[2])
+  int32_t nblk[2];      // 16-slot blocks in the nibble group (3/4-bit rows), in the dense 2-bit group (1/2-bit rows)
+  int32_t nslots;       // 16 * (nblk[0] + nblk[1])
+  int32_t words;        // uint32 words per tile = 256 nblk[0] + 128 nblk[1]
   int32_t tab_off;      // byte offset (from arena base) of [int16 rank[nslots] | fp16 s[nslots] | int16 row[nslots]]
-  int32_t pad_[2];
+  int32_t pad_[3];
 };
 
 struct FastExpert {
@@ -153,7 +153,7 @@ struct bm_layer {
   bm::ExpertDev* experts_dev = nullptr;  // in the arena
   void* arena = nullptr;
   size_t arena_bytes = 0;
-  bool fast_ok = false;            // every slab is 2/3/4-bit and shapes fit the decode / tensor paths
+  bool fast_ok = false;            // every slab is 1/2/3/4-bit and shapes fit the decode / tensor paths
   const bm::FastExpert* fast_dev = nullptr;   // in the arena
   std::vector<bm::FastExpert> fast_host;
   int max_unit_bytes = 0, max_slots = 0, max_words = 0;

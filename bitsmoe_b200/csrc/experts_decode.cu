@@ -4,11 +4,11 @@
 // gate, up and down for that tile, ~30 KB at the Qwen3-30B shape) is pulled into shared memory by
 // two cp.async.bulk copies that complete on mbarriers, so every active SM has its bytes in flight
 // from the first cycle; the down words land while gate/up are being consumed.  Weights never
-// exist as fp16 in memory: each warp rebuilds m16n8k16 A fragments from the bit-plane words in
-// registers (see fast_layout.cuh) and multiplies them with the tokens' activations (the B operand,
-// up to 16 assignments per pass) on the tensor cores.  The per-(tile,row) scale is folded into the
-// activation operand for gate/up and into the epilogue for down; the unsigned-code offset
-// 2^(b-1) is removed with a per-token correction term instead of per weight.  The six tiles of an
+// exist as fp16 in memory: each warp expands its arena words into m16n8k16 A fragments with one mask
+// per register (see fast_layout.cuh) and multiplies them with the tokens' activations (the B operand,
+// up to 8 assignments per pass) on the tensor cores.  The per-(tile,row) scale is folded into the
+// activation operand for gate/up and into the epilogue for down; the stored codes' offset
+// is removed with a per-token correction term instead of per weight.  The six tiles of an
 // expert split the contraction of the down product; their partial sums meet in rank_accum through
 // fp32 atomics (as in bitsmoe/algorithms/cpp/mlp_forward.cu:2036-2066).
 #include "fast_layout.cuh"
@@ -55,59 +55,61 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Four A-fragment registers (fp16 subnormals u * 2^-24) from the BITS plane words of one row pair.
-template <int BITS>
-__device__ __forceinline__ void planes_to_afrag(const uint32_t* __restrict__ w, int t, uint32_t (&a)[4]) {
-  uint32_t y0 = 0, y1 = 0;
-#pragma unroll
-  for (int p = 0; p < BITS; ++p) {
-    const uint32_t word = w[p];
-    y0 |= __funnelshift_r(word, word, (t - p) & 31) & (0x01010101u << p);
-    y1 |= __funnelshift_r(word, word, (t + 4 - p) & 31) & (0x01010101u << p);
-  }
-  a[0] = __byte_perm(y0, 0u, 0x4140);
-  a[1] = __byte_perm(y0, 0u, 0x4342);
-  a[2] = __byte_perm(y1, 0u, 0x4140);
-  a[3] = __byte_perm(y1, 0u, 0x4342);
+// Rows g + 8 of every A fragment carry a factor 16 (see fast_layout.cuh): accumulator registers 2 and 3
+// are scaled back with 2^20 instead of 2^24.
+constexpr float DEC_UNSCALE_LO = 16777216.f, DEC_UNSCALE_HI = 1048576.f;
+
+__device__ __forceinline__ void nib_afrag(uint32_t w, uint32_t (&a)[4]) {
+  const uint32_t s = w >> 8;
+  a[0] = w & 0x000F000Fu;
+  a[1] = w & 0x00F000F0u;
+  a[2] = s & 0x000F000Fu;
+  a[3] = s & 0x00F000F0u;
+}
+__device__ __forceinline__ void dense_afrag(uint32_t w, uint32_t (&a)[4]) {
+  const uint32_t s = w >> 2;
+  a[0] = w & 0x00030003u;
+  a[1] = w & 0x00300030u;
+  a[2] = s & 0x00030003u;
+  a[3] = s & 0x00300030u;
 }
 
-// One group of slot blocks of uniform width.  `words` points at the group's first word for this warp's
-// operand-row block; consecutive contraction blocks are `stride_kb` words apart; `bfrag` points at the
-// B operand row (assignment g of N-block 0) at the first contraction position of the group.
-// `off_acc` accumulates the same products against a constant A fragment whose every code is the
-// group's offset 2^(BITS-1): after the loop its column n holds offset * sum_k B[k][n] (times 2^-24),
-// the term that turns sum u*B into sum q*B.
-template <int BITS, int NB>
-__device__ __forceinline__ void mma_group(const uint32_t* __restrict__ words, int stride_kb, int nkb, int g, int t,
-                                          const __half* __restrict__ bop, int b_stride, float (&acc)[2][4],
-                                          float (&off_acc)[2][4]) {
-  const uint32_t* wp = words + g * BITS;
-  const __half* bp = bop + static_cast<size_t>(g) * b_stride + 2 * t;
-  constexpr uint32_t kOff = (1u << (BITS - 1)) * 0x00010001u;
-  const uint32_t offs[4] = {kOff, kOff, kOff, kOff};
+// `npairs` pairs of 16x16 blocks of one group against the token-side operand.  `wp` points at this lane's word(s) of
+// the first pair, consecutive pairs are `stride` words apart; `bp` points at this lane's eight halves of the first pair
+// (operand row g, position 8 t).  `off` accumulates the same products against a constant fragment holding the
+// group's code offset: its column n ends up as offset * sum_k B[k][n], the term that turns sum u*B into sum q*B.
+template <bool DENSE>
+__device__ __forceinline__ void mma_pairs(const uint32_t* __restrict__ wp, int stride, int npairs, const __half* __restrict__ bp,
+                                          float (&acc)[4], float (&off)[4]) {
+  constexpr uint32_t kLo = (DENSE ? FAST_DENSE_OFFSET : FAST_NIB_OFFSET) * 0x00010001u;
+  const uint32_t offs[4] = {kLo, kLo << 4, kLo, kLo << 4};
 #pragma unroll 2
-  for (int kb = 0; kb < nkb; ++kb) {
-    uint32_t w[BITS];
-#pragma unroll
-    for (int p = 0; p < BITS; ++p) w[p] = wp[p];
+  for (int p = 0; p < npairs; ++p) {
+    const uint4 b = *reinterpret_cast<const uint4*>(bp);
     uint32_t a[4];
-    planes_to_afrag<BITS>(w, t, a);
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-      const __half* b = bp + static_cast<size_t>(nb) * 8 * b_stride;
-      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(b), b1 = *reinterpret_cast<const uint32_t*>(b + 8);
-      mma_16816(acc[nb], a, b0, b1);
-      mma_16816(off_acc[nb], offs, b0, b1);
+    if (DENSE) {
+      const uint32_t w = *wp;
+      dense_afrag(w, a);
+      mma_16816(acc, a, b.x, b.y);
+      dense_afrag(w >> 8, a);
+      mma_16816(acc, a, b.z, b.w);
+    } else {
+      const uint2 w = *reinterpret_cast<const uint2*>(wp);
+      nib_afrag(w.x, a);
+      mma_16816(acc, a, b.x, b.y);
+      nib_afrag(w.y, a);
+      mma_16816(acc, a, b.z, b.w);
     }
-    wp += stride_kb;
-    bp += 16;
+    mma_16816(off, offs, b.x, b.y);
+    mma_16816(off, offs, b.z, b.w);
+    wp += stride;
+    bp += 32;
   }
 }
 
 struct DecSmem {
   unsigned char* unit;         // current unit block
-  const unsigned char* tabs;   // current expert's slot tables (copy of the arena region starting at tab_base)
-  int tab_base;                // arena offset the copy starts at
+  const unsigned char* tabs[3];   // current expert's [int16 rank | fp16 s] slot tables of gate, up, down
   __half* actp;                // [2][FAST_MAX_TOK][slots_stride]
   __half* zp;                  // [FAST_MAX_TOK][N_TILE + 8]
   int* tok;                    // [FAST_MAX_TOK]
@@ -120,13 +122,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
-constexpr int ZP_STRIDE = N_TILE + 8;   // halves; +8 keeps the B-fragment loads of 8 rows on distinct banks
+constexpr int ZP_STRIDE = N_TILE + 32;   // halves; rows 64 bytes apart modulo 128: the 16-byte operand loads of a quarter warp hit distinct banks
 
-__host__ __device__ inline int dec_slots_stride(int max_slots) { return max_slots + 8; }
+__host__ __device__ inline int dec_slots_stride(int max_slots) { return (max_slots + 63) / 64 * 64 + 32; }
 
 // One pipeline stage: [unit block | per-expert slot tables | h rows of the first pass's tokens (gate, up)]
 __host__ __device__ inline size_t dec_stage_bytes(int max_unit_bytes, int max_slots, int h_rank) {
-  return align_up_c(static_cast<size_t>(max_unit_bytes), 128) + align_up_c(static_cast<size_t>(3) * (max_slots * 6 + 16), 128) +
+  return align_up_c(static_cast<size_t>(max_unit_bytes), 128) + align_up_c(static_cast<size_t>(3) * (max_slots * 4 + 16), 128) +
          align_up_c(static_cast<size_t>(2) * FAST_MAX_TOK * h_rank * 2, 128);
 }
 
@@ -138,47 +140,37 @@ __host__ __device__ inline size_t dec_smem_bytes(int max_unit_bytes, int max_slo
   return align_up_c(o, 128);
 }
 
-template <int NB>
 __device__ __forceinline__ void decode_pass(const FastExpert& fe, const DecSmem& sm, int slots_stride, int tile, int n_valid,
                                             int npass, int rank_out, float* __restrict__ rank_accum,
                                             const unsigned char* __restrict__ arena, uint64_t* bar_down, uint32_t parity,
                                             bool* ok, long long& bm_tick_, int* bm_timing_base) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   // ---- gate / up: this warp owns columns 16*warp .. 16*warp+15 of the tile
-  float acc[2][2][4], offa[2][2][4];
+  float acc[2][4], offa[2][4];
 #pragma unroll
   for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[m][nb][j] = offa[m][nb][j] = 0.f;
+    for (int j = 0; j < 4; ++j) acc[m][j] = offa[m][j] = 0.f;
 #pragma unroll
   for (int m = 0; m < 2; ++m) {
     const FastMat& fm = fe.m[m];
     const uint32_t* sec = reinterpret_cast<const uint32_t*>(sm.unit + fe.sec_off[3 + m]);
-    const __half* bop = sm.actp + static_cast<size_t>(m) * FAST_MAX_TOK * slots_stride;
-    // [kb][mblock][g][plane]: a contraction block holds 64*b words, this warp's rows start at warp*8*b
-    mma_group<4, NB>(sec + warp * 8 * 4, 64 * 4, fm.nblk[0], g, t, bop, slots_stride, acc[m], offa[m]);
-    sec += fm.nblk[0] * 64 * 4;
-    bop += fm.nblk[0] * 16;
-    mma_group<3, NB>(sec + warp * 8 * 3, 64 * 3, fm.nblk[1], g, t, bop, slots_stride, acc[m], offa[m]);
-    sec += fm.nblk[1] * 64 * 3;
-    bop += fm.nblk[1] * 16;
-    mma_group<2, NB>(sec + warp * 8 * 2, 64 * 2, fm.nblk[2], g, t, bop, slots_stride, acc[m], offa[m]);
+    const __half* bop = sm.actp + static_cast<size_t>(m) * FAST_MAX_TOK * slots_stride + static_cast<size_t>(g) * slots_stride + 8 * t;
+    // nibble words [pair][x][lane][2], dense words [pair][x][lane]
+    mma_pairs<false>(sec + (warp * 32 + lane) * 2, 512, fm.nblk[0] >> 1, bop, acc[m], offa[m]);
+    mma_pairs<true>(sec + fm.nblk[0] * 256 + warp * 32 + lane, 256, fm.nblk[1] >> 1, bop + fm.nblk[0] * 16, acc[m], offa[m]);
   }
   BM_TICK(3);
   // ---- z = silu(g) * u, written as the down product's B operand
 #pragma unroll
-  for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int c = 16 * warp + g + (j >= 2 ? 8 : 0);
-      const int n = nb * 8 + 2 * t + (j & 1);
-      const float gv = (acc[0][nb][j] - offa[0][nb][j]) * 16777216.f;
-      const float uv = (acc[1][nb][j] - offa[1][nb][j]) * 16777216.f;
-      const float z = (c < n_valid && n < npass) ? (gv / (1.f + __expf(-gv))) * uv : 0.f;
-      sm.zp[n * ZP_STRIDE + (c & ~15) + kperm16(c & 15)] = __float2half_rn(z);
-    }
+  for (int j = 0; j < 4; ++j) {
+    const int c = 16 * warp + g + (j >= 2 ? 8 : 0);
+    const int n = 2 * t + (j & 1);
+    const float unscale = j >= 2 ? DEC_UNSCALE_HI : DEC_UNSCALE_LO;
+    const float gv = (acc[0][j] - offa[0][j]) * unscale;
+    const float uv = (acc[1][j] - offa[1][j]) * unscale;
+    const float z = (c < n_valid && n < npass) ? (gv / (1.f + __expf(-gv))) * uv : 0.f;
+    sm.zp[n * ZP_STRIDE + slot_pos(c)] = __float2half_rn(z);
   }
   consumer_sync();
   BM_TICK(4);
@@ -188,38 +180,30 @@ __device__ __forceinline__ void decode_pass(const FastExpert& fe, const DecSmem&
   const FastMat& fd = fe.m[2];
   const uint32_t* dwords = reinterpret_cast<const uint32_t*>(sm.unit + fe.sec_off[5]);
   const __half* scale_d = reinterpret_cast<const __half*>(sm.unit + fe.sec_off[2]);
-  const int16_t* rank_d = reinterpret_cast<const int16_t*>(sm.tabs + (fd.tab_off - sm.tab_base));
-  const __half* s_d = reinterpret_cast<const __half*>(sm.tabs + (fd.tab_off - sm.tab_base) + fd.nslots * 2);
+  const int16_t* rank_d = reinterpret_cast<const int16_t*>(sm.tabs[2]);
+  const __half* s_d = reinterpret_cast<const __half*>(sm.tabs[2] + fd.nslots * 2);
   const int nblk_total = fd.nslots >> 4;
+  const __half* zrow = sm.zp + g * ZP_STRIDE + 8 * t;
   for (int mb = warp; mb < nblk_total; mb += 8) {
-    float dacc[2][4], doff[2][4];
+    float dacc[4], doff[4];
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) dacc[nb][j] = doff[nb][j] = 0.f;
-    if (mb < fd.nblk[0]) {
-      mma_group<4, NB>(dwords + mb * 64 * 4, 8 * 4, 8, g, t, sm.zp, ZP_STRIDE, dacc, doff);
-    } else if (mb < fd.nblk[0] + fd.nblk[1]) {
-      mma_group<3, NB>(dwords + fd.nblk[0] * 64 * 4 + (mb - fd.nblk[0]) * 64 * 3, 8 * 3, 8, g, t, sm.zp, ZP_STRIDE, dacc, doff);
-    } else {
-      mma_group<2, NB>(dwords + fd.nblk[0] * 64 * 4 + fd.nblk[1] * 64 * 3 + (mb - fd.nblk[0] - fd.nblk[1]) * 64 * 2, 8 * 2, 8, g,
-                       t, sm.zp, ZP_STRIDE, dacc, doff);
-    }
+    for (int j = 0; j < 4; ++j) dacc[j] = doff[j] = 0.f;
+    // nibble words [mblock][pair][lane][2], dense words [mblock][pair][lane]
+    if (mb < fd.nblk[0]) mma_pairs<false>(dwords + (mb * 128 + lane) * 2, 64, 4, zrow, dacc, doff);
+    else mma_pairs<true>(dwords + fd.nblk[0] * 256 + (mb - fd.nblk[0]) * 128 + lane, 32, 4, zrow, dacc, doff);
 #pragma unroll
     for (int half_rows = 0; half_rows < 2; ++half_rows) {
       const int slot = mb * 16 + g + 8 * half_rows;
       const int rk = rank_d[slot];
       if (rk < 0 || rk >= rank_out) continue;
-      const float f = __half2float(s_d[slot]) * __half2float(scale_d[slot]) * 16777216.f;
+      const float f = __half2float(s_d[slot]) * __half2float(scale_d[slot]) * (half_rows ? DEC_UNSCALE_HI : DEC_UNSCALE_LO);
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int n = nb * 8 + 2 * t + h;
-          if (n >= npass) continue;
-          const float v = (dacc[nb][2 * half_rows + h] - doff[nb][2 * half_rows + h]) * f * sm.rw[n];
-          atomicAdd(&rank_accum[static_cast<int64_t>(sm.tok[n]) * rank_out + rk], v);
-        }
+      for (int h = 0; h < 2; ++h) {
+        const int n = 2 * t + h;
+        if (n >= npass) continue;
+        const float v = (dacc[2 * half_rows + h] - doff[2 * half_rows + h]) * f * sm.rw[n];
+        atomicAdd(&rank_accum[static_cast<int64_t>(sm.tok[n]) * rank_out + rk], v);
+      }
     }
   }
 }
@@ -251,15 +235,14 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
   __shared__ int warp_cnt[9];
   const int slots_stride = dec_slots_stride(max_slots);
   const size_t unit_bytes_al = align_up_c(static_cast<size_t>(max_unit_bytes), 128);
-  const size_t tabs_bytes_al = align_up_c(static_cast<size_t>(3) * (max_slots * 6 + 16), 128);
+  const size_t tabs_bytes_al = align_up_c(static_cast<size_t>(3) * (max_slots * 4 + 16), 128);
   const size_t stage_bytes = dec_stage_bytes(max_unit_bytes, max_slots, h_rank);
   DecSmem sm;
   int16_t* active;
   {
     size_t o = 2 * stage_bytes;
     sm.unit = smem_raw;
-    sm.tabs = nullptr;
-    sm.tab_base = 0;
+    sm.tabs[0] = sm.tabs[1] = sm.tabs[2] = nullptr;
     sm.actp = reinterpret_cast<__half*>(smem_raw + o);
     o += static_cast<size_t>(2) * FAST_MAX_TOK * slots_stride * 2;
     sm.zp = reinterpret_cast<__half*>(smem_raw + o);
@@ -326,13 +309,15 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
       const unsigned char* src = arena + fe.unit_base + static_cast<int64_t>(tile) * fe.unit_bytes;
       const uint32_t bytes_a = static_cast<uint32_t>(fe.sec_off[5]);
       const uint32_t bytes_b = static_cast<uint32_t>(fe.m[2].words) * 4u;
-      const int tab0 = fe.m[0].tab_off;
-      const uint32_t tab_bytes = static_cast<uint32_t>(fe.m[2].tab_off + static_cast<int>(align_up_c(fe.m[2].nslots * 6, 16)) - tab0);
+      const uint32_t tb0 = static_cast<uint32_t>(fe.m[0].nslots) * 4u, tb1 = static_cast<uint32_t>(fe.m[1].nslots) * 4u,
+                     tb2 = static_cast<uint32_t>(fe.m[2].nslots) * 4u;   // [rank | s] of each matrix, the row table stays behind
       const uint32_t row_bytes = static_cast<uint32_t>(h_rank) * 2u;
       if (lane == 0) {
-        mbar_expect_tx(&bar_full[buf][0], bytes_a + tab_bytes + 2u * npass * row_bytes);
+        mbar_expect_tx(&bar_full[buf][0], bytes_a + tb0 + tb1 + tb2 + 2u * npass * row_bytes);
         bulk_g2s(stage, src, bytes_a, &bar_full[buf][0]);
-        bulk_g2s(stage + unit_bytes_al, arena + tab0, tab_bytes, &bar_full[buf][0]);
+        bulk_g2s(stage + unit_bytes_al, arena + fe.m[0].tab_off, tb0, &bar_full[buf][0]);
+        bulk_g2s(stage + unit_bytes_al + tb0, arena + fe.m[1].tab_off, tb1, &bar_full[buf][0]);
+        bulk_g2s(stage + unit_bytes_al + tb0 + tb1, arena + fe.m[2].tab_off, tb2, &bar_full[buf][0]);
         mbar_expect_tx(&bar_full[buf][1], bytes_b);
         bulk_g2s(stage + bytes_a, src + bytes_a, bytes_b, &bar_full[buf][1]);
       }
@@ -364,8 +349,9 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
     const FastExpert& fe = si.fe;
     DecSmem cur = sm;
     cur.unit = stage;
-    cur.tabs = stage + unit_bytes_al;
-    cur.tab_base = fe.m[0].tab_off;
+    cur.tabs[0] = stage + unit_bytes_al;
+    cur.tabs[1] = cur.tabs[0] + fe.m[0].nslots * 4;
+    cur.tabs[2] = cur.tabs[1] + fe.m[1].nslots * 4;
     cur.tok = si.tok;
     cur.rw = si.rw;
     const __half* hrows = reinterpret_cast<const __half*>(stage + unit_bytes_al + tabs_bytes_al);
@@ -389,15 +375,15 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
         const int nslots = fe.m[m].nslots;
-        const int16_t* rank_t = reinterpret_cast<const int16_t*>(cur.tabs + (fe.m[m].tab_off - cur.tab_base));
-        const __half* s_t = reinterpret_cast<const __half*>(cur.tabs + (fe.m[m].tab_off - cur.tab_base) + nslots * 2);
+        const int16_t* rank_t = reinterpret_cast<const int16_t*>(cur.tabs[m]);
+        const __half* s_t = reinterpret_cast<const __half*>(cur.tabs[m] + nslots * 2);
         const __half* scale_t = reinterpret_cast<const __half*>(stage + fe.sec_off[m]);
         const __half* hg = m == 0 ? h_gate : h_up;
         const __half* hs = hrows + static_cast<size_t>(m) * FAST_MAX_TOK * h_rank;
         __half* dst = cur.actp + static_cast<size_t>(m) * FAST_MAX_TOK * slots_stride;
         for (int slot = threadIdx.x; slot < nslots; slot += DEC_CONSUMERS) {
           const int rk = rank_t[slot];
-          const int pos = (slot & ~15) + kperm16(slot & 15);
+          const int pos = slot_pos(slot);
           const float f = __half2float(s_t[slot]) * __half2float(scale_t[pos]);
           const bool live = rk >= 0 && rk < h_rank;
           float hv[FAST_MAX_TOK];
@@ -413,7 +399,7 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
       }
       consumer_sync();
       BM_TICK(1);
-      decode_pass<1>(fe, cur, slots_stride, tile, n_valid, npass, rank_out, rank_accum, arena, &bar_full[buf][1], parity, &ok,
+      decode_pass(fe, cur, slots_stride, tile, n_valid, npass, rank_out, rank_accum, arena, &bar_full[buf][1], parity, &ok,
                      bm_tick_, bm_timing_base);
       BM_TICK(6);
     }
@@ -439,7 +425,14 @@ int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half*
     BM_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, L->device));
     attr_set_for = L->device;
   }
-  const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+  static size_t occ_for_smem = 0;
+  static int per_sm = 1;
+  if (occ_for_smem != smem) {
+    int blocks = 1;
+    BM_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, experts_decode_kernel, DEC_THREADS, smem));
+    per_sm = blocks < 1 ? 1 : (blocks > 2 ? 2 : blocks);
+    occ_for_smem = smem;
+  }
   int grid = sm_count * per_sm;
   const int max_units = L->num_experts * L->n_tiles;
   if (grid > max_units) grid = max_units;

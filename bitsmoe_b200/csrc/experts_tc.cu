@@ -40,8 +40,8 @@ constexpr int XT_THREADS = 576;
 constexpr int XT_EPI_WARPS = 8, XT_PRODUCER_WARP = 8, XT_MMA_WARP = 9, XT_DQ_WARP0 = 10, XT_DQ_WARPS = 8;
 constexpr int XT_RING = 4;                // A-operand stages
 constexpr int XT_STAGE_BLOCKS = 4;        // contraction blocks of 16 per stage (one per dequantiser warp pair)
-constexpr int XT_BLOCK_BYTES = 128 * 16 * 2;
-constexpr int XT_STAGE_BYTES = XT_STAGE_BLOCKS * XT_BLOCK_BYTES;
+constexpr int XT_A_CHUNK = 128 * 16 + 32;  // bytes between 8-position chunks of a weight stage (padded: conflict-free 16-byte stores)
+constexpr int XT_STAGE_BYTES = 2 * XT_STAGE_BLOCKS * XT_A_CHUNK;
 constexpr int XT_CHUNK_STRIDE = XT_NT * 16 + 16;   // bytes between 8-position chunks of the token-side operands (padded: conflict-free stores)
 constexpr int XT_MAX_E = 1024;
 constexpr int XT_SEC = 5;                 // section slots: (tile, matrix) sections up to five ahead
@@ -80,60 +80,42 @@ __device__ __forceinline__ bool xt_wait(uint64_t* bar, uint32_t parity, volatile
   }
 }
 
-// 32 codes of a row pair (rows g and g+8 of a 16-row block, 16 contraction positions) -> fp16 values
-// (u - offset) * scale, as four 16-byte chunks: row g positions 0-7 / 8-15, row g+8 positions 0-7 / 8-15 of the
-// block in the order k = (0,8,1,9,2,10,3,11 | 4,12,5,13,6,14,7,15).  `sc_lo[s]` = scale pair applied to the
-// register holding positions (s, s+8) of row g, `sc_hi[s]` the same for row g+8.
-template <int BITS>
-__device__ __forceinline__ void dequant_rowpair(const uint32_t* __restrict__ w, const __half2* sc_lo, const __half2* sc_hi,
-                                                uint4& g_c0, uint4& g_c1, uint4& h_c0, uint4& h_c1) {
-  uint32_t words[BITS];
-#pragma unroll
-  for (int p = 0; p < BITS; ++p) words[p] = w[p];
-  const uint32_t bias_bits = 0x64006400u + (1u << (BITS - 1)) * 0x00010001u;   // fp16x2 of 1024 + offset
-  const __half2 bias = *reinterpret_cast<const __half2*>(&bias_bits);
-  // phase-major so that the eight position chains issue back to back instead of one after the other
-  uint32_t y[8], lo[8], hi[8];
-#pragma unroll
-  for (int s = 0; s < 8; ++s) y[s] = __funnelshift_r(words[0], words[0], s & 31) & 0x01010101u;
-#pragma unroll
-  for (int p = 1; p < BITS; ++p) {
-#pragma unroll
-    for (int s = 0; s < 8; ++s) y[s] |= __funnelshift_r(words[p], words[p], (s - p) & 31) & (0x01010101u << p);
-  }
-#pragma unroll
-  for (int s = 0; s < 8; ++s) {
-    lo[s] = __byte_perm(y[s], 0x64646464u, 0x4140);   // (1024 + u) for row g,   positions s, s+8
-    hi[s] = __byte_perm(y[s], 0x64646464u, 0x4342);   // (1024 + u) for row g+8, positions s, s+8
-  }
-  __half2 va[8], vb[8];
-#pragma unroll
-  for (int s = 0; s < 8; ++s) {
-    va[s] = __hsub2(*reinterpret_cast<const __half2*>(&lo[s]), bias);
-    vb[s] = __hsub2(*reinterpret_cast<const __half2*>(&hi[s]), bias);
-  }
-#pragma unroll
-  for (int s = 0; s < 8; ++s) {
-    va[s] = __hmul2(va[s], sc_lo[s]);
-    vb[s] = __hmul2(vb[s], sc_hi[s]);
-    lo[s] = *reinterpret_cast<uint32_t*>(&va[s]);
-    hi[s] = *reinterpret_cast<uint32_t*>(&vb[s]);
-  }
-  g_c0 = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-  g_c1 = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-  h_c0 = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-  h_c1 = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+// One arena word (a 16x16 block's codes owned by lane (g, t), see fast_layout.cuh) -> four fp16 pairs
+// (q * scale): r[0] = row g, k (2t, 2t+1); r[1] = row g+8, same k; r[2] = row g, k (2t+8, 2t+9); r[3] = row g+8.
+// The code sits in the mantissa of 1024 (fields at bit 0) or of 64 (fields at bit 4); subtracting
+// 1024 + offset or 64 + offset is exact, the multiplication by the scale rounds once, as fp16(q * scale) does.
+template <bool DENSE>
+__device__ __forceinline__ void dequant_block(uint32_t w, __half2 s0, __half2 s1, __half2 s2, __half2 s3, uint32_t (&r)[4]) {
+  constexpr uint32_t mlo = DENSE ? 0x00030003u : 0x000F000Fu, mhi = DENSE ? 0x00300030u : 0x00F000F0u;
+  constexpr uint32_t off = DENSE ? FAST_DENSE_OFFSET : FAST_NIB_OFFSET;
+  constexpr uint32_t blo_bits = 0x64006400u + off * 0x00010001u;          // fp16x2 of 1024 + offset
+  constexpr uint32_t bhi_bits = 0x54005400u + off * 0x00100010u;          // fp16x2 of 64 + offset
+  const uint32_t blo_u = blo_bits, bhi_u = bhi_bits;
+  const __half2 blo = *reinterpret_cast<const __half2*>(&blo_u), bhi = *reinterpret_cast<const __half2*>(&bhi_u);
+  const uint32_t sh = w >> (DENSE ? 2 : 8);
+  uint32_t v[4] = {(w & mlo) | 0x64006400u, (w & mhi) | 0x54005400u, (sh & mlo) | 0x64006400u, (sh & mhi) | 0x54005400u};
+  const __half2 o0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v[0]), blo), s0);
+  const __half2 o1 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v[1]), bhi), s1);
+  const __half2 o2 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v[2]), blo), s2);
+  const __half2 o3 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v[3]), bhi), s3);
+  r[0] = *reinterpret_cast<const uint32_t*>(&o0);
+  r[1] = *reinterpret_cast<const uint32_t*>(&o1);
+  r[2] = *reinterpret_cast<const uint32_t*>(&o2);
+  r[3] = *reinterpret_cast<const uint32_t*>(&o3);
 }
 
-// Writes one row-pair unit (mblock x, row g) of an A-operand stage: rows 16x+g and 16x+g+8, two K chunks.
-__device__ __forceinline__ void store_unit(unsigned char* stage, int x, int g, const uint4& g_c0, const uint4& g_c1,
-                                           const uint4& h_c0, const uint4& h_c1) {
-  unsigned char* p = stage + (2 * x) * 128 + g * 16;
-  *reinterpret_cast<uint4*>(p) = g_c0;
-  *reinterpret_cast<uint4*>(p + 2048) = g_c1;
-  *reinterpret_cast<uint4*>(p + 128) = h_c0;
-  *reinterpret_cast<uint4*>(p + 128 + 2048) = h_c1;
+// The two blocks of a pair -> the two 16-byte chunks (rows 16x+g and 16x+g+8) of K-chunk 4*pair_in_stage + t.
+// `word0` / `word1` are the pair's two blocks (dense: the same word, the second shifted by 8).
+template <bool DENSE>
+__device__ __forceinline__ void dequant_pair_store(uint32_t word0, uint32_t word1, const __half2 (&sa)[4], const __half2 (&sb)[4],
+                                                   unsigned char* dst) {
+  uint32_t r0[4], r1[4];
+  dequant_block<DENSE>(word0, sa[0], sb[0], sa[1], sb[1], r0);
+  dequant_block<DENSE>(word1, sa[2], sb[2], sa[3], sb[3], r1);
+  *reinterpret_cast<uint4*>(dst) = make_uint4(r0[0], r0[2], r1[0], r1[2]);
+  *reinterpret_cast<uint4*>(dst + 128) = make_uint4(r0[1], r0[3], r1[1], r1[3]);
 }
+
 struct XtSmem {
   unsigned char* act;     // [2][nchunks][XT_NT rows] canonical K-major, 16-byte chunks
   unsigned char* z;       // [16 chunks][XT_NT rows]
@@ -291,8 +273,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
           __half hv[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const int q = (c8 & 1) * 8 + j;                      // position inside the 16-block
-            slot[j] = (c8 >> 1) * 16 + ((q & 7) >> 1) + 8 * (q & 1) + ((q >> 3) << 2);
+            slot[j] = ((c8 >> 2) << 5) + pos32_inv((c8 & 3) * 8 + j);   // chunk c8 = positions 8 c8 .. 8 c8 + 7 of the pos32 order
             hv[j] = hrow[rk_s[slot[j]]];
           }
           __half v[8];
@@ -333,7 +314,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         const uint32_t act_base = tc::smem_u32(sm.act), z_base = tc::smem_u32(sm.z), ring_base = tc::smem_u32(sm.ring);
         const uint32_t act_m_bytes = static_cast<uint32_t>(max_slots / 8) * XT_CHUNK_STRIDE;
         // descriptors: constant upper part, start-address field advanced per block
-        const uint64_t a_desc0 = tc::smem_desc_kmajor(ring_base, 2048, 128);
+        const uint64_t a_desc0 = tc::smem_desc_kmajor(ring_base, XT_A_CHUNK, 128);
         const uint64_t b_desc0 = tc::smem_desc_kmajor(act_base, XT_CHUNK_STRIDE, 128);
         const uint64_t z_desc0 = tc::smem_desc_kmajor(z_base, XT_CHUNK_STRIDE, 128);
         for (int tile = 0; tile < n_tiles && ok; ++tile, ++gr) {
@@ -348,7 +329,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
               tc::fence_after_sync();
               const int cnt = min(XT_STAGE_BLOCKS, nkb - kb0);
               for (int j = 0; j < cnt; ++j) {
-                const uint64_t ad = a_desc0 + ((slot * XT_STAGE_BYTES + j * XT_BLOCK_BYTES) >> 4);
+                const uint64_t ad = a_desc0 + ((slot * XT_STAGE_BYTES + 2 * j * XT_A_CHUNK) >> 4);
                 const uint64_t bd = bm_desc + ((2 * (kb0 + j) * XT_CHUNK_STRIDE) >> 4);
                 tc::mma_f16(m == 0 ? d_gate : d_up, ad, bd, idesc, (kb0 + j) > 0 ? 1u : 0u);
               }
@@ -366,7 +347,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
               if (!(ok = xt_wait(&bars.w_full[slot], (ri / XT_RING) & 1, abort_flag))) break;
               tc::fence_after_sync();
               for (int j = 0; j < XT_STAGE_BLOCKS; ++j) {
-                const uint64_t ad = a_desc0 + ((slot * XT_STAGE_BYTES + j * XT_BLOCK_BYTES) >> 4);
+                const uint64_t ad = a_desc0 + ((slot * XT_STAGE_BYTES + 2 * j * XT_A_CHUNK) >> 4);
                 const uint64_t bd = z_desc0 + ((2 * (kb0 + j) * XT_CHUNK_STRIDE) >> 4);
                 tc::mma_f16(d_down + mt * XT_NT, ad, bd, idesc, (tile > 0 || kb0 + j > 0) ? 1u : 0u);
               }
@@ -380,11 +361,11 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
     }
     else if (warp >= XT_DQ_WARP0) {
       // ------------------------------------------------------------------ dequantisers
-      const int dw = warp - XT_DQ_WARP0, tid_d = threadIdx.x - XT_DQ_WARP0 * 32;
+      const int dw = warp - XT_DQ_WARP0;
       XT_TICK_INIT();
-      // Two teams of four warps take alternate stages; inside a team warp `wt` converts block `wt` of the
-      // stage, two row-pair units per thread (independent chains), so two stages are always in flight.
-      const int team = dw >> 2, wt = dw & 3;
+      // Two teams of four warps take alternate stages (two pairs of 16-blocks x 128 operand rows); inside a team
+      // warp `wt` converts the operand-row blocks x = wt and wt + 4, so two stages are always in flight.
+      const int team = dw >> 2, wt = dw & 3, g = lane >> 2, t = lane & 3;
       uint32_t ri = ring_i, sr = sec_round;
       bool ok = true;
       for (int tile = 0; tile < n_tiles && ok; ++tile, ++sr) {
@@ -394,31 +375,36 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
           if (!ok) break;
           const FastMat& fm = fe.m[m];
           const uint32_t* words = reinterpret_cast<const uint32_t*>(sm.sec[ss] + sec_scale_bytes);
-          const __half2* scale2 = reinterpret_cast<const __half2*>(sm.sec[ss]);
-          const int nkb = fm.nslots >> 4;
-          const int e4 = fm.nblk[0], e3 = fm.nblk[0] + fm.nblk[1];
-          for (int kb0 = 0; kb0 < nkb; kb0 += XT_STAGE_BLOCKS, ++ri) {
+          const uint4* scale4 = reinterpret_cast<const uint4*>(sm.sec[ss]);    // 8 halves per (pair, t)
+          const int npairs = fm.nslots >> 5, nib_pairs = fm.nblk[0] >> 1;
+          const uint32_t* dense_words = words + fm.nblk[0] * 256;
+          for (int p0 = 0; p0 < npairs; p0 += 2, ++ri) {
             if (static_cast<int>(ri & 1u) != team) continue;
             const int slot = ri % XT_RING;
             if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
-            const int kb = kb0 + wt;
-            if (kb < nkb) {
-              int b, boff;
-              if (kb < e4) { b = 4; boff = kb * 256; }
-              else if (kb < e3) { b = 3; boff = e4 * 256 + (kb - e4) * 192; }
-              else { b = 2; boff = e4 * 256 + (e3 - e4) * 192 + (kb - e3) * 128; }
-              const __half2* sc = scale2 + kb * 8;
-              unsigned char* dst = sm.ring + slot * XT_STAGE_BYTES + wt * XT_BLOCK_BYTES;
-              const uint32_t* w0 = words + boff + lane * b;            // unit = lane      -> x = lane >> 3, g = lane & 7
-              const uint32_t* w1 = w0 + 32 * b;                         // unit = lane + 32 -> x + 4
-              uint4 c0, c1, d0, d1, e0, e1, f0, f1;
-              if (b == 4) { dequant_rowpair<4>(w0, sc, sc, c0, c1, d0, d1); dequant_rowpair<4>(w1, sc, sc, e0, e1, f0, f1); }
-              else if (b == 3) { dequant_rowpair<3>(w0, sc, sc, c0, c1, d0, d1); dequant_rowpair<3>(w1, sc, sc, e0, e1, f0, f1); }
-              else { dequant_rowpair<2>(w0, sc, sc, c0, c1, d0, d1); dequant_rowpair<2>(w1, sc, sc, e0, e1, f0, f1); }
-              store_unit(dst, lane >> 3, lane & 7, c0, c1, d0, d1);
-              store_unit(dst, (lane >> 3) + 4, lane & 7, e0, e1, f0, f1);
-              tc::fence_async_smem();
+            unsigned char* stage = sm.ring + slot * XT_STAGE_BYTES;
+#pragma unroll
+            for (int pp = 0; pp < 2; ++pp) {
+              const int pr = p0 + pp;
+              if (pr >= npairs) break;
+              const uint4 sv = scale4[pr * 4 + t];
+              const __half2 sc[4] = {*reinterpret_cast<const __half2*>(&sv.x), *reinterpret_cast<const __half2*>(&sv.y),
+                                     *reinterpret_cast<const __half2*>(&sv.z), *reinterpret_cast<const __half2*>(&sv.w)};
+              unsigned char* dst = stage + (pp * 4 + t) * XT_A_CHUNK + g * 16;
+              if (pr < nib_pairs) {
+                const uint2 w0 = reinterpret_cast<const uint2*>(words)[(pr * 8 + wt) * 32 + lane];
+                const uint2 w1 = reinterpret_cast<const uint2*>(words)[(pr * 8 + wt + 4) * 32 + lane];
+                dequant_pair_store<false>(w0.x, w0.y, sc, sc, dst + wt * 256);
+                dequant_pair_store<false>(w1.x, w1.y, sc, sc, dst + (wt + 4) * 256);
+              } else {
+                const int dp = pr - nib_pairs;
+                const uint32_t w0 = dense_words[(dp * 8 + wt) * 32 + lane];
+                const uint32_t w1 = dense_words[(dp * 8 + wt + 4) * 32 + lane];
+                dequant_pair_store<true>(w0, w0 >> 8, sc, sc, dst + wt * 256);
+                dequant_pair_store<true>(w1, w1 >> 8, sc, sc, dst + (wt + 4) * 256);
+              }
             }
+            tc::fence_async_smem();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&bars.w_full[slot]);
           }
@@ -431,42 +417,46 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         if (!ok) break;
         const FastMat& fd = fe.m[2];
         const uint32_t* dwords = reinterpret_cast<const uint32_t*>(sm.sec[sd] + sec_scale_bytes);
+        const uint32_t* ddense = dwords + fd.nblk[0] * 256;
         const __half* scale_d = reinterpret_cast<const __half*>(sm.sec[sd]);
         for (int mt = 0; mt < n_mt && ok; ++mt) {
-          // this thread's two units: row-pair g of slot blocks 8*mt + x and 8*mt + x + 4
-          int bb[2], bo[2];
+          // this thread's two operand-row blocks: slot blocks 8*mt + wt and 8*mt + wt + 4
           __half2 sg[2], sh[2];
+          int mbu[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int mb = 8 * mt + (lane >> 3) + 4 * u, g = lane & 7;
-            bb[u] = 0; bo[u] = 0;
+            mbu[u] = 8 * mt + wt + 4 * u;
             sg[u] = sh[u] = __float2half2_rn(0.f);
-            if (mb < nblk_d) {
-              if (mb < fd.nblk[0]) { bb[u] = 4; bo[u] = mb * 256; }
-              else if (mb < fd.nblk[0] + fd.nblk[1]) { bb[u] = 3; bo[u] = fd.nblk[0] * 256 + (mb - fd.nblk[0]) * 192; }
-              else { bb[u] = 2; bo[u] = fd.nblk[0] * 256 + fd.nblk[1] * 192 + (mb - fd.nblk[0] - fd.nblk[1]) * 128; }
-              sg[u] = __half2half2(scale_d[16 * mb + g]);
-              sh[u] = __half2half2(scale_d[16 * mb + g + 8]);
+            if (mbu[u] < nblk_d) {
+              sg[u] = __half2half2(scale_d[16 * mbu[u] + g]);
+              sh[u] = __half2half2(scale_d[16 * mbu[u] + g + 8]);
             }
           }
-          for (int kb0 = 0; kb0 < 8; kb0 += XT_STAGE_BLOCKS, ++ri) {
+          for (int p0 = 0; p0 < 4; p0 += 2, ++ri) {
             if (static_cast<int>(ri & 1u) != team) continue;
             const int slot = ri % XT_RING;
             if (!(ok = xt_wait(&bars.w_empty[slot], ((ri / XT_RING) & 1) ^ 1, abort_flag))) break;
-            const int kb = kb0 + wt, g = lane & 7;
-            unsigned char* dst = sm.ring + slot * XT_STAGE_BYTES + wt * XT_BLOCK_BYTES;
+            unsigned char* stage = sm.ring + slot * XT_STAGE_BYTES;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              uint4 c0 = make_uint4(0, 0, 0, 0), c1 = c0, d0 = c0, d1 = c0;
-              if (bb[u]) {
-                const uint32_t* w = dwords + bo[u] + (kb * 8 + g) * bb[u];
-                const __half2 sgl[8] = {sg[u], sg[u], sg[u], sg[u], sg[u], sg[u], sg[u], sg[u]};
-                const __half2 shl[8] = {sh[u], sh[u], sh[u], sh[u], sh[u], sh[u], sh[u], sh[u]};
-                if (bb[u] == 4) dequant_rowpair<4>(w, sgl, shl, c0, c1, d0, d1);
-                else if (bb[u] == 3) dequant_rowpair<3>(w, sgl, shl, c0, c1, d0, d1);
-                else dequant_rowpair<2>(w, sgl, shl, c0, c1, d0, d1);
+            for (int pp = 0; pp < 2; ++pp) {
+              const int pr = p0 + pp;
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                unsigned char* dst = stage + (pp * 4 + t) * XT_A_CHUNK + g * 16 + (wt + 4 * u) * 256;
+                const __half2 sa[4] = {sg[u], sg[u], sg[u], sg[u]};
+                const __half2 sb[4] = {sh[u], sh[u], sh[u], sh[u]};
+                const int mb = mbu[u];
+                if (mb >= nblk_d) {
+                  *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                  *reinterpret_cast<uint4*>(dst + 128) = make_uint4(0, 0, 0, 0);
+                } else if (mb < fd.nblk[0]) {
+                  const uint2 w = reinterpret_cast<const uint2*>(dwords)[(mb * 4 + pr) * 32 + lane];
+                  dequant_pair_store<false>(w.x, w.y, sa, sb, dst);
+                } else {
+                  const uint32_t w = ddense[((mb - fd.nblk[0]) * 4 + pr) * 32 + lane];
+                  dequant_pair_store<true>(w, w >> 8, sa, sb, dst);
+                }
               }
-              store_unit(dst, (lane >> 3) + 4 * u, g, c0, c1, d0, d1);
             }
             tc::fence_async_smem();
             __syncwarp();
@@ -484,7 +474,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
       bool ok = true;
       XT_TICK_INIT();
       const int c = 32 * q + lane;                                   // row of D_g / D_u = column of the tile
-      const int c_pos = (c & ~15) + kperm16(c & 15);
+      const int c_pos = slot_pos(c);
       unsigned char* zrow = sm.z + (c_pos >> 3) * XT_CHUNK_STRIDE + (c_pos & 7) * 2;
       for (int tile = 0; tile < n_tiles && ok; ++tile, ++gr) {
         ok = xt_wait(&bars.gu_done, gr & 1, abort_flag, 200);
