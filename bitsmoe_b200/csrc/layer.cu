@@ -32,6 +32,8 @@ struct SkinnyArgs {
   int round_x_f16;
   int splits;
   int mrows;
+  float4* zero;
+  int zero_n;
 };
 int launch_skinny_nt(SkinnyArgs a, cudaStream_t st);
 constexpr int SKINNY_MAX_TOKENS = 256;
@@ -379,8 +381,11 @@ extern "C" int bm_layer_decode_codes(const bm_layer_t* L, int32_t e, int32_t whi
   return BM_OK;
 }
 
-extern "C" int bm_basis_project(const bm_layer_t* L, const void* x, int x_dtype, int32_t T, uint16_t* h_gate,
-                                uint16_t* h_up, void* stream) {
+// `zero` / `zero_bytes`: a buffer (16-byte multiple) the projection kernel clears as a side job; `*zeroed` tells
+// the caller whether the path taken did it.
+static int basis_project_impl(const bm_layer_t* L, const void* x, int x_dtype, int32_t T, uint16_t* h_gate, uint16_t* h_up,
+                              void* zero, size_t zero_bytes, bool* zeroed, void* stream) {
+  if (zeroed) *zeroed = false;
   BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "basis_project: null layer");
   BM_REQUIRE(L->vh_gate && L->vh_up, BM_ERR_INVALID_ARG, "missing shared_vh basis for packed routed experts");
   BM_REQUIRE(T >= 0 && x_dtype >= BM_F16 && x_dtype <= BM_F32, BM_ERR_INVALID_ARG, "basis_project: bad arguments");
@@ -396,6 +401,11 @@ extern "C" int bm_basis_project(const bm_layer_t* L, const void* x, int x_dtype,
     a.N = T; a.K = L->hidden;
     a.x_dtype = x_dtype; a.c_dtype = BM_F16; a.round_x_f16 = 1;
     a.splits = 8; a.mrows = 32;
+    if (zero != nullptr && zero_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(zero) & 15u) == 0 && zero_bytes / 16 < (1u << 30)) {
+      a.zero = static_cast<float4*>(zero);
+      a.zero_n = static_cast<int>(zero_bytes / 16);
+      if (zeroed) *zeroed = true;
+    }
     return launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
   }
   if (L->hidden % 64 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && !getenv("BM_NO_TC")) {
@@ -420,23 +430,27 @@ extern "C" int bm_basis_project(const bm_layer_t* L, const void* x, int x_dtype,
   return launch_gemm_nt(g, 2, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int bm_basis_project(const bm_layer_t* L, const void* x, int x_dtype, int32_t T, uint16_t* h_gate,
+                                uint16_t* h_up, void* stream) {
+  return basis_project_impl(L, x, x_dtype, T, h_gate, h_up, nullptr, 0, nullptr, stream);
+}
+
 extern "C" size_t bm_experts_workspace_bytes(const bm_layer_t* L, int32_t T, int32_t num_assign, int32_t path) {
   (void)L; (void)T; (void)num_assign; (void)path;
   return 0;
 }
 
-extern "C" int bm_experts_forward(const bm_layer_t* L, const uint16_t* h_gate, const uint16_t* h_up,
-                                  const int32_t* token_indices, const int32_t* expert_offsets,
-                                  const float* route_weights, int32_t T, int32_t num_assign, float* rank_accum,
-                                  int32_t path, void* workspace, size_t workspace_bytes, void* stream) {
-  (void)workspace; (void)workspace_bytes;
+static int experts_forward_impl(const bm_layer_t* L, const uint16_t* h_gate, const uint16_t* h_up,
+                                const int32_t* token_indices, const int32_t* expert_offsets, const float* route_weights,
+                                int32_t T, int32_t num_assign, float* rank_accum, int32_t path, bool already_zero,
+                                void* stream) {
   BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "experts_forward: null layer");
   BM_REQUIRE(T >= 0 && num_assign >= 0, BM_ERR_INVALID_ARG, "experts_forward: negative sizes");
   BM_REQUIRE(path >= BM_PATH_AUTO && path <= BM_PATH_TENSOR, BM_ERR_INVALID_ARG, "experts_forward: unknown path %d", path);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (T == 0) return BM_OK;
   BM_REQUIRE(rank_accum, BM_ERR_INVALID_ARG, "experts_forward: null rank_accum");
-  BM_CUDA(cudaMemsetAsync(rank_accum, 0, sizeof(float) * static_cast<size_t>(T) * L->rank_out, st));
+  if (!already_zero) BM_CUDA(cudaMemsetAsync(rank_accum, 0, sizeof(float) * static_cast<size_t>(T) * L->rank_out, st));
   if (num_assign == 0 || L->num_experts == 0) return BM_OK;
   BM_REQUIRE(h_gate && h_up && token_indices && expert_offsets && route_weights, BM_ERR_INVALID_ARG,
              "experts_forward: null pointer");
@@ -452,6 +466,15 @@ extern "C" int bm_experts_forward(const bm_layer_t* L, const uint16_t* h_gate, c
                                  token_indices, expert_offsets, route_weights, T, rank_accum, st);
   return launch_experts_generic(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
                                 token_indices, expert_offsets, route_weights, T, rank_accum, st);
+}
+
+extern "C" int bm_experts_forward(const bm_layer_t* L, const uint16_t* h_gate, const uint16_t* h_up,
+                                  const int32_t* token_indices, const int32_t* expert_offsets,
+                                  const float* route_weights, int32_t T, int32_t num_assign, float* rank_accum,
+                                  int32_t path, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  return experts_forward_impl(L, h_gate, h_up, token_indices, expert_offsets, route_weights, T, num_assign, rank_accum, path,
+                              false, stream);
 }
 
 extern "C" int bm_combine_down_basis(const bm_layer_t* L, const float* rank_accum, int32_t T, const void* residual,
@@ -522,8 +545,13 @@ extern "C" int bm_layer_forward(const bm_layer_t* L, const void* x, int x_dtype,
   int rc = bm_route(logits, logits_dtype, T, num_routed, k, renorm, weight_round, global_to_local, L->num_experts, TILE_ROWS,
                     w.topk_idx, w.topk_w, w.token_indices, w.expert_offsets, w.route_flat, w.tile_table, w.counts, w.route_ws,
                     w.route_ws_bytes, route_stream);
-  const int rc_basis =
-      bm_basis_project(L, x, x_dtype, T, reinterpret_cast<uint16_t*>(w.h_gate), reinterpret_cast<uint16_t*>(w.h_up), stream);
+  // the accumulator of the expert stage is cleared off the critical path: by the projection kernel when the
+  // skinny one runs, else by a memset beside the routing
+  bool zeroed = false;
+  const size_t acc_bytes = sizeof(float) * static_cast<size_t>(T) * L->rank_out;
+  const int rc_basis = basis_project_impl(L, x, x_dtype, T, reinterpret_cast<uint16_t*>(w.h_gate),
+                                          reinterpret_cast<uint16_t*>(w.h_up), w.rank_accum, acc_bytes, &zeroed, stream);
+  if (!zeroed && cudaMemsetAsync(w.rank_accum, 0, acc_bytes, static_cast<cudaStream_t>(route_stream)) == cudaSuccess) zeroed = true;
   if (fork) {
     // always join, also on error, so that the side stream never stays attached to a capture
     cudaEventRecord(L->ev_join, L->side_stream);
@@ -533,9 +561,8 @@ extern "C" int bm_layer_forward(const bm_layer_t* L, const void* x, int x_dtype,
   if (rc_basis) return rc_basis;
   // Dropped assignments (experts that are not packed) leave a shorter list; the kernels walk
   // expert_offsets, so passing the upper bound T*k as num_assign is safe.
-  rc = bm_experts_forward(L, reinterpret_cast<const uint16_t*>(w.h_gate), reinterpret_cast<const uint16_t*>(w.h_up),
-                          w.token_indices, w.expert_offsets, w.route_flat, T, T * k, w.rank_accum, path, w.experts_ws,
-                          w.experts_ws_bytes, stream);
+  rc = experts_forward_impl(L, reinterpret_cast<const uint16_t*>(w.h_gate), reinterpret_cast<const uint16_t*>(w.h_up),
+                            w.token_indices, w.expert_offsets, w.route_flat, T, T * k, w.rank_accum, path, zeroed, stream);
   if (rc) return rc;
   return bm_combine_down_basis(L, w.rank_accum, T, residual, y, x_dtype == BM_F32 ? BM_F32 : x_dtype, stream);
 }

@@ -28,6 +28,8 @@ struct SkinnyArgs {
   int round_x_f16;       // X is fp32 and is rounded through fp16 (always true for fp32 here)
   int splits;            // cluster size along k
   int mrows;             // W rows per CTA: 16 or 32
+  float4* zero;          // optional buffer the grid clears on its way (the next kernel's accumulator), 16-byte units
+  int zero_n;
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -59,38 +61,60 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_nt_kernel(SkinnyArgs a) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(W + static_cast<size_t>(r) * a.K + c) : "memory");
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
+  if (a.zero != nullptr) {
+    for (int i = blockIdx.x * SK_THREADS + threadIdx.x; i < a.zero_n; i += gridDim.x * SK_THREADS) a.zero[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const int mblocks = a.mrows / 16;
   for (int n0 = 0; n0 < a.N; n0 += SK_NTOK) {
     const int nn = min(SK_NTOK, a.N - n0);
     const int nblocks = (nn + 7) / 8;
     __syncthreads();   // previous chunk's readers of Xs / part are done
-    // X slice -> fp16 smem
-    for (int v = threadIdx.x; v < nblocks * 8 * vec_per_row; v += SK_THREADS) {
-      const int r = v / vec_per_row, c = (v - r * vec_per_row) * 8;
-      __half out[8];
-      if (r < nn) {
-        const size_t idx = static_cast<size_t>(n0 + r) * a.K + static_cast<size_t>(split) * ks + c;
-        if (a.x_dtype == BM_F16) {
-          *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(a.X) + idx);
-        } else if (a.x_dtype == BM_BF16) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.X) + idx);
-          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    // X slice -> fp16 smem; the loads of four vectors are issued before the first conversion
+    const int nvec = nblocks * 8 * vec_per_row;
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * SK_THREADS) {
+      uint4 raw[4][2];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + u * SK_THREADS;
+        const int r = v / vec_per_row, c = (v - r * vec_per_row) * 8;
+        raw[u][0] = raw[u][1] = make_uint4(0u, 0u, 0u, 0u);
+        if (v < nvec && r < nn) {
+          const size_t idx = static_cast<size_t>(n0 + r) * a.K + static_cast<size_t>(split) * ks + c;
+          if (a.x_dtype == BM_F32) {
+            raw[u][0] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(a.X) + idx);
+            raw[u][1] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(a.X) + idx + 4);
+          } else {
+            raw[u][0] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.X) + idx);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + u * SK_THREADS;
+        if (v >= nvec) break;
+        const int r = v / vec_per_row, c = (v - r * vec_per_row) * 8;
+        uint4 out = raw[u][0];
+        if (a.x_dtype == BM_BF16) {
+          const uint32_t w[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
+          uint32_t o[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            out[2 * i] = __float2half_rn(__uint_as_float(w[i] << 16));
-            out[2 * i + 1] = __float2half_rn(__uint_as_float(w[i] & 0xffff0000u));
+            const __half2 h2 = __floats2half2_rn(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+            o[i] = *reinterpret_cast<const uint32_t*>(&h2);
           }
-        } else {
-          const float4 f0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.X) + idx);
-          const float4 f1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.X) + idx + 4);
-          out[0] = __float2half_rn(f0.x); out[1] = __float2half_rn(f0.y); out[2] = __float2half_rn(f0.z); out[3] = __float2half_rn(f0.w);
-          out[4] = __float2half_rn(f1.x); out[5] = __float2half_rn(f1.y); out[6] = __float2half_rn(f1.z); out[7] = __float2half_rn(f1.w);
-        }
-      } else {
+          out = make_uint4(o[0], o[1], o[2], o[3]);
+        } else if (a.x_dtype == BM_F32) {
+          const uint32_t w[8] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w, raw[u][1].x, raw[u][1].y, raw[u][1].z, raw[u][1].w};
+          uint32_t o[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) out[i] = __float2half(0.f);
+          for (int i = 0; i < 4; ++i) {
+            const __half2 h2 = __floats2half2_rn(__uint_as_float(w[2 * i]), __uint_as_float(w[2 * i + 1]));
+            o[i] = *reinterpret_cast<const uint32_t*>(&h2);
+          }
+          out = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        *reinterpret_cast<uint4*>(Xs + static_cast<size_t>(r) * stride + c) = out;
       }
-      *reinterpret_cast<uint4*>(Xs + static_cast<size_t>(r) * stride + c) = *reinterpret_cast<uint4*>(out);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
@@ -135,11 +159,10 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_nt_kernel(SkinnyArgs a) {
       const int total = a.mrows * nblocks * 8;
       for (int o = split + a.splits * threadIdx.x; o < total; o += a.splits * SK_THREADS) {
         const int m = o % a.mrows, n = o / a.mrows;
-        float v = 0.f;
-        for (int r = 0; r < a.splits; ++r) {
-          const float* remote = cluster.map_shared_rank(part, r);
-          v += remote[m * (SK_NTOK + 1) + n];
-        }
+        float pv[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) pv[r] = r < a.splits ? cluster.map_shared_rank(part, r)[m * (SK_NTOK + 1) + n] : 0.f;
+        float v = ((pv[0] + pv[1]) + (pv[2] + pv[3])) + ((pv[4] + pv[5]) + (pv[6] + pv[7]));
         if (n < nn) {
           const size_t idx = static_cast<size_t>(n0 + n) * a.rows_per_w + mloc0 + m;
           if (a.residual && wsel == 0) v += load_act(a.residual, a.c_dtype, idx);
@@ -153,7 +176,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_nt_kernel(SkinnyArgs a) {
 
 // Returns BM_ERR_UNSUPPORTED when the shape does not fit; the caller then uses the general GEMM.
 int launch_skinny_nt(SkinnyArgs a, cudaStream_t st) {
-  BM_REQUIRE(a.K % (16 * a.splits) == 0 && a.rows_per_w % a.mrows == 0, BM_ERR_UNSUPPORTED, "skinny_nt: shape does not tile");
+  BM_REQUIRE(a.K % (16 * a.splits) == 0 && a.rows_per_w % a.mrows == 0 && a.splits <= 8, BM_ERR_UNSUPPORTED, "skinny_nt: shape does not tile");
   const int ks = a.K / a.splits;
   size_t smem = static_cast<size_t>(a.mrows + SK_NTOK) * (ks + 8) * 2;
   if (a.splits > 1) smem += static_cast<size_t>(a.mrows) * (SK_NTOK + 1) * 4;
