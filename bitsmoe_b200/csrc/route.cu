@@ -17,50 +17,95 @@ constexpr int ROUTE_WARPS = ROUTE_BLOCK / 32;
 
 // ---------------------------------------------------------------- top-k
 // One warp per token; probabilities live in a warp-private shared row.
-// Top-k of one token by one warp; `p` is a warp-private shared row of E floats.
+// Top-k of one token by one warp.  Up to ROUTE_REG_E experts stay in registers (lane l holds experts l, l+32, ...);
+// `p` is a warp-private shared row of E floats used only beyond that.
+constexpr int ROUTE_REG_PER_LANE = 8;
+constexpr int ROUTE_REG_E = 32 * ROUTE_REG_PER_LANE;
+
 __device__ __forceinline__ void warp_topk_token(const void* __restrict__ logits, int dtype, int t, int E, int k, int renorm,
                                                 int weight_round, float* p, int32_t* __restrict__ idx_out,
                                                 float* __restrict__ w_out) {
   const int lane = threadIdx.x & 31;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) {
-    const float v = load_act(logits, dtype, static_cast<int64_t>(t) * E + e);
-    p[e] = v;
-    mx = fmaxf(mx, v);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float v = expf(p[e] - mx);
-    p[e] = v;
-    sum += v;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  const float inv = 1.f / sum;
-  __syncwarp();
   float my_w = 0.f;   // lane j keeps the j-th selected weight (k <= 32)
   int my_i = 0;
   float wsum = 0.f;
-  for (int j = 0; j < k; ++j) {
-    float best = -1.f;
-    int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = p[e];
-      if (v > best) { best = v; bi = e; }   // strided scan visits ascending e: first hit wins ties
+  if (E <= ROUTE_REG_E) {
+    float v[ROUTE_REG_PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ROUTE_REG_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      v[i] = e < E ? load_act(logits, dtype, static_cast<int64_t>(t) * E + e) : -INFINITY;
+      mx = fmaxf(mx, v[i]);
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < ROUTE_REG_PER_LANE; ++i) {
+      v[i] = lane + 32 * i < E ? expf(v[i] - mx) : -1.f;   // padding can never win
+      sum += fmaxf(v[i], 0.f);
     }
-    const float w = best * inv;
-    if (lane == j) { my_w = w; my_i = bi; }
-    wsum += w;
-    if (lane == 0) p[bi] = -2.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+    for (int j = 0; j < k; ++j) {
+      float best = -1.f;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < ROUTE_REG_PER_LANE; ++i)
+        if (v[i] > best) { best = v[i]; bi = lane + 32 * i; }   // ascending e: the first hit wins ties
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+      }
+      const float w = best * inv;
+      if (lane == j) { my_w = w; my_i = bi; }
+      wsum += w;
+#pragma unroll
+      for (int i = 0; i < ROUTE_REG_PER_LANE; ++i)
+        if (bi == lane + 32 * i) v[i] = -2.f;
+    }
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) {
+      const float v = load_act(logits, dtype, static_cast<int64_t>(t) * E + e);
+      p[e] = v;
+      mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float v = expf(p[e] - mx);
+      p[e] = v;
+      sum += v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
     __syncwarp();
+    for (int j = 0; j < k; ++j) {
+      float best = -1.f;
+      int bi = 0x7fffffff;
+      for (int e = lane; e < E; e += 32) {
+        const float v = p[e];
+        if (v > best) { best = v; bi = e; }   // strided scan visits ascending e: first hit wins ties
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+      }
+      const float w = best * inv;
+      if (lane == j) { my_w = w; my_i = bi; }
+      wsum += w;
+      if (lane == 0) p[bi] = -2.f;
+      __syncwarp();
+    }
   }
   if (lane < k) {
     float w = renorm ? my_w / wsum : my_w;
@@ -226,39 +271,6 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) route_build_fused_kernel(
   write_tile_table(s.scan, E, tile_rows, tile_table, max_tiles, counts, reinterpret_cast<int*>(s.warp_base), s.block_count);
 }
 
-// T*k <= ROUTE_BLOCK: top-k of every token and the whole permutation in one block, one launch.
-__global__ void __launch_bounds__(ROUTE_BLOCK) route_all_fused_kernel(
-    const void* __restrict__ logits, int dtype, int T, int E_routed, int k, int renorm, int weight_round,
-    const int32_t* __restrict__ g2l, int E, int tile_rows, int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
-    int32_t* __restrict__ token_indices, int32_t* __restrict__ expert_offsets, float* __restrict__ route_flat,
-    int32_t* __restrict__ tile_table, int max_tiles, int32_t* __restrict__ counts) {
-  extern __shared__ __align__(16) unsigned char sm_raw[];
-  RouteSmem s = carve_route_smem(sm_raw, E);
-  float* prob = reinterpret_cast<float*>(sm_raw + route_smem_bytes_dev(E));   // [ROUTE_WARPS][E_routed]
-  const int warp = threadIdx.x >> 5;
-  for (int t = warp; t < T; t += ROUTE_WARPS)
-    warp_topk_token(logits, dtype, t, E_routed, k, renorm, weight_round, prob + warp * E_routed, topk_idx, topk_w);
-  __threadfence_block();
-  __syncthreads();
-  const int A = T * k;
-  const int i = threadIdx.x;
-  int e = -1;
-  if (i < A) {
-    e = topk_idx[i];
-    if (g2l) e = g2l[e];
-  }
-  const int rank_w = block_count_and_rank(e, E, s);
-  block_exclusive_scan(s.block_count, s.scan, E);
-  for (int x = threadIdx.x; x <= E; x += blockDim.x) expert_offsets[x] = s.scan[x];
-  if (e >= 0) {
-    const int pos = s.scan[e] + s.warp_base[(threadIdx.x >> 5) * E + e] + rank_w;
-    token_indices[pos] = i / k;
-    route_flat[pos] = topk_w[i];
-  }
-  __syncthreads();
-  write_tile_table(s.scan, E, tile_rows, tile_table, max_tiles, counts, reinterpret_cast<int*>(s.warp_base), s.block_count);
-}
-
 // A > ROUTE_BLOCK: count per block, scan across blocks, scatter.
 __global__ void __launch_bounds__(ROUTE_BLOCK) route_count_kernel(const int32_t* __restrict__ topk_idx,
                                                                  const int32_t* __restrict__ g2l, int A, int E,
@@ -406,24 +418,6 @@ extern "C" int bm_route(const void* logits, int logits_dtype, int32_t T, int32_t
                         float* route_flat, int32_t* tile_table, int32_t* counts, void* workspace, size_t workspace_bytes,
                         void* stream) {
   using namespace bm;
-  const int64_t A = static_cast<int64_t>(T) * k;
-  const size_t fused_smem = route_smem_bytes(num_local > 0 ? num_local : 1) + sizeof(float) * ROUTE_WARPS * (E_routed > 0 ? E_routed : 1);
-  if (T > 0 && A <= ROUTE_BLOCK && E_routed > 0 && E_routed <= ROUTE_MAX_E && num_local > 0 && num_local <= ROUTE_MAX_E &&
-      k > 0 && k <= 32 && k <= E_routed && tile_rows > 0 && fused_smem <= 200 * 1024) {
-    BM_REQUIRE(logits && topk_idx && topk_w && token_indices && expert_offsets && route_flat, BM_ERR_INVALID_ARG,
-               "route: null pointer");
-    BM_REQUIRE(logits_dtype >= BM_F16 && logits_dtype <= BM_F32, BM_ERR_INVALID_ARG, "route: bad logits dtype");
-    static bool attr_done = false;
-    if (!attr_done) {
-      BM_CUDA(cudaFuncSetAttribute(route_all_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      attr_done = true;
-    }
-    route_all_fused_kernel<<<1, ROUTE_BLOCK, fused_smem, static_cast<cudaStream_t>(stream)>>>(
-        logits, logits_dtype, T, E_routed, k, renorm, weight_round, global_to_local, num_local, tile_rows, topk_idx, topk_w,
-        token_indices, expert_offsets, route_flat, tile_table, bm_route_max_tiles(T, k, num_local, tile_rows), counts);
-    BM_LAUNCH_CHECK("route_all_fused_kernel");
-    return BM_OK;
-  }
   int rc = bm_route_topk(logits, logits_dtype, T, E_routed, k, renorm, weight_round, topk_idx, topk_w, stream);
   if (rc) return rc;
   return bm_route_build(topk_idx, topk_w, global_to_local, T, k, num_local, tile_rows, token_indices, expert_offsets,

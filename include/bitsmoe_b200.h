@@ -150,7 +150,7 @@ BM_API int bm_route_build_static(const int32_t* topk_idx, const float* topk_w, c
                                  int32_t* token_indices, int32_t* expert_offsets, float* route_flat,
                                  int32_t* tile_table, int32_t* counts, void* stream);
 
-/* Router tail and routing build in one call (a single launch when T*k <= 1024): the sequence
+/* Router tail and routing build in one call (bm_route_topk then bm_route_build): the sequence
  * bitsmoe/models/qwen3moe/bitsmoe_block.py:47-51 -> bitsmoe/models/base_block.py:258-289. */
 BM_API int bm_route(const void* logits, int logits_dtype, int32_t T, int32_t E_routed, int32_t k, int32_t renorm,
                     int32_t weight_round, const int32_t* global_to_local, int32_t num_local, int32_t tile_rows,
