@@ -39,6 +39,10 @@ def parse():
     ap.add_argument("--prefill-tokens", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="headline only (skip other batch sizes / prefill / cpu)")
     ap.add_argument("--path", type=int, default=0, help="experts path: 0 auto, 1 generic, 2 decode, 3 tensor")
+    ap.add_argument("--probe", default=None, choices=["experts", "forward"],
+                    help="no timing: run the packed-experts stage or the whole layer forward --steps times over --layers "
+                         "rotating weight sets with --tokens tokens (Zipf(1.1) routing above 256 tokens) and exit; the "
+                         "target of profiler captures")
     return ap.parse_args()
 
 
@@ -197,6 +201,37 @@ def active_expert_bytes(packed, offsets_cpu):
             n += packed.expert_bytes(e)
             act += 1
     return n, act
+
+
+def probe(args):
+    """Small fixed workload for profiler captures (one GPU): see --probe."""
+    from bitsmoe_b200 import synth
+    from bitsmoe_b200.layer import route_build, route_topk
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = synth.QWEN3_30B
+    T, L = args.tokens, args.layers
+    layers = [synth.to_packed_layer(synth.make_layer(cfg, seed=42 + i, device=dev), dev) for i in range(L)]
+    zipf = 1.1 if T > 256 else None
+    prep = []
+    for i in range(L):
+        x = synth.activations(cfg, T, seed=7 + i, device=dev)
+        lg = synth.router_logits(cfg, T, seed=9 + i, device=dev) if zipf is None else \
+            synth.router_logits(cfg, T, seed=9 + i, zipf_s=zipf, device=dev)
+        idx, w = route_topk(lg, cfg.top_k, True, torch.bfloat16)
+        tok, off, rw, _, _ = route_build(idx, w, cfg.num_experts)
+        hg, hu = layers[i].basis_project(x)
+        prep.append((x, lg, hg, hu, tok, off, rw))
+    torch.cuda.synchronize(dev)
+    for it in range(args.steps):
+        i = it % L
+        if args.probe == "experts":
+            layers[i].experts_forward(*prep[i][2:], path=args.path)
+        else:
+            layers[i].forward(prep[i][0], prep[i][1], cfg.top_k, True, torch.bfloat16, path=args.path)
+    torch.cuda.synchronize(dev)
+    layers[0].check_status()
+    print(json.dumps({"probe": args.probe, "tokens": T, "layers": L, "steps": args.steps}), flush=True)
 
 
 def gpu_arm(args):
@@ -399,5 +434,7 @@ if __name__ == "__main__":
     a = parse()
     if a.impl == "reference":
         reference_arm(a)
+    elif a.probe:
+        probe(a)
     else:
         gpu_arm(a)
