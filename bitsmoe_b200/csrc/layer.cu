@@ -455,12 +455,12 @@ static int experts_forward_impl(const bm_layer_t* L, const uint16_t* h_gate, con
   BM_REQUIRE(h_gate && h_up && token_indices && expert_offsets && route_weights, BM_ERR_INVALID_ARG,
              "experts_forward: null pointer");
   BM_REQUIRE(path != BM_PATH_TENSOR || L->fast_ok, BM_ERR_UNSUPPORTED,
-             "experts_forward: the tensor path needs 2/3/4-bit rows and full tiles; this layer has neither");
+             "experts_forward: the tensor path needs 1- to 4-bit rows and full tiles; this layer has neither");
   if (L->fast_ok && (path == BM_PATH_TENSOR || (path == BM_PATH_AUTO && num_assign > 16 * L->num_experts && !getenv("BM_NO_TC"))))
     return launch_experts_tc(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up), token_indices,
                              expert_offsets, route_weights, T, rank_accum, st);
   BM_REQUIRE(path != BM_PATH_DECODE || L->fast_ok, BM_ERR_UNSUPPORTED,
-             "experts_forward: the decode path needs 2/3/4-bit rows and full tiles; this layer has neither");
+             "experts_forward: the decode path needs 1- to 4-bit rows and full tiles; this layer has neither");
   if (L->fast_ok && path != BM_PATH_GENERIC)
     return launch_experts_decode(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
                                  token_indices, expert_offsets, route_weights, T, rank_accum, st);

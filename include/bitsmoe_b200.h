@@ -104,7 +104,7 @@ BM_API int64_t bm_layer_expert_bytes(const bm_layer_t* layer, int32_t expert);
 BM_API int bm_layer_decode_codes(const bm_layer_t* layer, int32_t expert, int32_t which, int32_t source, int8_t* codes,
                                  void* stream);
 /* 1 when the layer was repacked into the arena layout that the decode and tensor paths need
- * (every stored row 2, 3 or 4 bits wide, full tiles), else 0. */
+ * (every stored row 1 to 4 bits wide, full tiles), else 0. */
 BM_API int bm_layer_has_fast_layout(const bm_layer_t* layer);
 /* Synchronises `stream` and reports whether any kernel of this layer gave up a bounded wait since
  * the last call (BM_ERR_TIMEOUT) -- the device-side counterpart of C10_CUDA_KERNEL_LAUNCH_CHECK. */
