@@ -39,6 +39,9 @@ def parse():
     ap.add_argument("--prefill-tokens", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="headline only (skip other batch sizes / prefill / cpu)")
     ap.add_argument("--path", type=int, default=0, help="experts path: 0 auto, 1 generic, 2 decode, 3 tensor")
+    ap.add_argument("--parallel", default="dp", choices=["dp", "ep"],
+                    help="with --gpus N > 1: dp = every rank runs the whole layer on its own tokens (weights replicated, "
+                         "no data-path collective); ep = experts sharded over the ranks, rank-space exchange over NCCL")
     ap.add_argument("--probe", default=None, choices=["experts", "forward"],
                     help="no timing: run the packed-experts stage or the whole layer forward --steps times over --layers "
                          "rotating weight sets with --tokens tokens (Zipf(1.1) routing above 256 tokens) and exit; the "
@@ -246,7 +249,8 @@ def gpu_arm(args):
     cfg = synth.QWEN3_30B
     pk = peaks()
     L = args.layers
-    if world > 1:
+    use_ep = world > 1 and args.parallel == "ep"
+    if use_ep:
         from bitsmoe_b200 import ep
 
         class _EpAdapter:
@@ -277,8 +281,9 @@ def gpu_arm(args):
             sync()
 
     def decode_case(T, steps, warmup, want_roofline):
-        xs = [synth.activations(cfg, T, seed=7 + i, device=dev) for i in range(L)]
-        lg = [synth.router_logits(cfg, T, seed=9 + i, device=dev) for i in range(L)]
+        # every rank draws its own tokens
+        xs = [synth.activations(cfg, T, seed=7 + i + 1000 * rank, device=dev) for i in range(L)]
+        lg = [synth.router_logits(cfg, T, seed=9 + i + 1000 * rank, device=dev) for i in range(L)]
         ys = [torch.empty_like(xs[0]) for _ in range(L)]
         step = lambda i: layers[i % L].forward(xs[i % L], lg[i % L], cfg.top_k, True, torch.bfloat16, out=ys[i % L], path=args.path)
         for i in range(max(warmup, 3)):
@@ -286,7 +291,7 @@ def gpu_arm(args):
         barrier()
         ms = timed(step, steps, sync, use_graph=True)
         out = {"tokens": T, "ms_per_step": ms / steps, "tokens_per_s": T * steps / (ms * 1e-3)}
-        if want_roofline and world > 1:
+        if want_roofline and use_ep:
             out.update(experts_kernel_ms=None, experts_bytes=None, active_experts=None)
         elif want_roofline:
             # dominant kernel alone: the packed-experts stage on prepared routing, same rotation
@@ -318,8 +323,8 @@ def gpu_arm(args):
         device buffers, so step i+1's upload and step i-1's download overlap step i's kernels, as a serving loop
         would arrange them; the whole pipeline is one CUDA graph."""
         NB = 2
-        hx = [synth.activations(cfg, T, seed=70 + i).pin_memory() for i in range(4)]
-        hl = [synth.router_logits(cfg, T, seed=90 + i).pin_memory() for i in range(4)]
+        hx = [synth.activations(cfg, T, seed=70 + i + 1000 * rank).pin_memory() for i in range(4)]
+        hl = [synth.router_logits(cfg, T, seed=90 + i + 1000 * rank).pin_memory() for i in range(4)]
         hy = [torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(NB)]
         dx = [torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=dev) for _ in range(NB)]
         dl = [torch.empty((T, cfg.num_experts), dtype=torch.float32, device=dev) for _ in range(NB)]
@@ -399,9 +404,12 @@ def gpu_arm(args):
         ms_step = float(mx[0])
         value = world * args.tokens / (ms_step * 1e-3)
         e2e["value"] = float(mn[1]) * world
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
     if rank != 0:
         return
-    achieved = head["experts_bytes"] / (head["experts_kernel_ms"] * 1e-3) / 1e9 if world == 1 else None
+    achieved = head["experts_bytes"] / (head["experts_kernel_ms"] * 1e-3) / 1e9 if not use_ep else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
@@ -412,7 +420,9 @@ def gpu_arm(args):
                    "l2": f"inputs larger than L2: {L} distinct weight sets of ~23 MB rotate through the timed loop",
                    "launch": "all timed steps captured in one CUDA graph, replayed once inside the CUDA-event bracket",
                    "parallelism": "1 GPU" if world == 1 else
-                   f"ep{world}: experts sharded over {world} GPUs, rank-space all_gather dispatch / reduce_scatter combine (NCCL), captured in the same CUDA graph"},
+                   (f"ep{world}: experts sharded over {world} GPUs, rank-space all_gather dispatch / reduce_scatter combine (NCCL), captured in the same CUDA graph"
+                    if use_ep else
+                    f"dp{world}: every GPU runs the whole layer on its own {args.tokens} tokens, weights replicated, no data-path collective")},
         "e2e": e2e, "gpu_launches": 5 * args.steps, "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": (achieved / pk["hbm_gbs"]) if achieved else None, "traffic": None, "peak_source": pk["source"],
