@@ -142,6 +142,11 @@ def time_cpu(layer, tokens, steps, warmup):
     return tokens / dt, dt, cores
 
 
+def workload_name(tokens):
+    return (f"qwen3-30b-a3b moe layer decode, {tokens} tokens per GPU, mixed 2/3/4-bit (0.8/0.15/0.05), "
+            "rank-256 shared basis, top-8 of 128 experts")
+
+
 def reference_arm(args):
     rank, world, _ = dist_env(args)
     if rank != 0:
@@ -156,8 +161,8 @@ def reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"qwen3-30b-a3b moe layer decode, {args.tokens} tokens, mixed 2/3/4-bit (0.8/0.15/0.05)",
-                   "tokens": args.tokens, "experts": cfg.num_experts, "top_k": cfg.top_k},
+        "config": {"workload": workload_name(args.tokens), "tokens_per_gpu": args.tokens,
+                   "sample": "one layer on the host cores of rank 0; the GPU arm's step on the same shapes"},
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{steps} forwards of one layer, {args.tokens} tokens, dequantise-then-matmul fp32"},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -414,8 +419,7 @@ def gpu_arm(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": f"qwen3-30b-a3b moe layer decode, {args.tokens} tokens per GPU, mixed 2/3/4-bit "
-                               "(0.8/0.15/0.05), rank-256 shared basis, top-8 of 128 experts",
+        "config": {"workload": workload_name(args.tokens),
                    "tokens_per_gpu": args.tokens, "layers_rotated": L,
                    "l2": f"inputs larger than L2: {L} distinct weight sets of ~23 MB rotate through the timed loop",
                    "launch": "all timed steps captured in one CUDA graph, replayed once inside the CUDA-event bracket",
