@@ -314,3 +314,36 @@ def test_tensor_path_vs_oracle(q30_small, T):
     faithful = oforward.packed_forward(o["h_gate"], o["h_up"], o["token_indices"], o["expert_offsets"], o["route_flat"],
                                        experts, layer.cfg.rank, mode="faithful")
     helpers.assert_close(got, faithful, rtol=1e-2, atol=3e-4, what="rank_accum (tensor path) vs fp16-faithful oracle")
+
+
+@pytest.fixture(scope="module")
+def low_bits():
+    """1-, 2-, 3- and 4-bit rows in one layer: both word formats of the arena (nibble and dense 2-bit), with group
+    sizes that need padding to whole 32-slot pairs."""
+    cfg = synth.LayerConfig("lowbits-8e", 512, 8, 384, 2, rank=112, bit_probs=((1, 0.2), (2, 0.35), (3, 0.3), (4, 0.15)))
+    layer = synth.make_layer(cfg, seed=23, device=DEV)
+    return layer, synth.to_packed_layer(layer, DEV), helpers.decoded_experts(layer)
+
+
+def test_arena_holds_one_bit_rows(low_bits):
+    layer, packed, _ = low_bits
+    assert packed.has_fast_layout
+    for which, tag in enumerate(("gate", "up", "down")):
+        for e in (0, 3, 7):
+            want = opacker.decode_matrix(helpers.table_entry(layer, tag, e), layer.cfg.intermediate)["codes"]
+            assert np.array_equal(packed.decode_codes(e, which, source=1).cpu().numpy(), want), (tag, e, "arena")
+
+
+@pytest.mark.parametrize("path", [capi.PATH_DECODE, capi.PATH_TENSOR])
+@pytest.mark.parametrize("T", [3, 40])
+def test_one_to_four_bit_rows_on_fast_paths(low_bits, T, path):
+    layer, packed, experts = low_bits
+    x, logits = _inputs(layer, T, 300 + T)
+    o = oforward.layer_forward(x, logits, layer.vh_gate.cpu(), layer.vh_up.cpu(), layer.u_down.cpu(), experts,
+                               layer.cfg.top_k)
+    args = [o[k].to(DEV) for k in ("h_gate", "h_up", "token_indices", "expert_offsets", "route_flat")]
+    got = packed.experts_forward(*args, path=path)
+    packed.check_status()
+    helpers.assert_close(got, o["rank_accum"], rtol=1e-2, atol=3e-4, what="rank_accum (1-4 bit rows) vs fp32 oracle")
+    gen = packed.experts_forward(*args, path=capi.PATH_GENERIC)
+    helpers.assert_close(got, gen, rtol=1e-2, atol=3e-4, what="fast path vs generic path, 1-4 bit rows")
