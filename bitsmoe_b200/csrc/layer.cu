@@ -48,9 +48,6 @@ struct GemmTcArgs {
 };
 int launch_gemm_tc(const GemmTcArgs& a, int problems, cudaStream_t st);
 void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P);
-int launch_route_ticket_fused(const void* logits, int logits_dtype, int T, int E_routed, int k, int renorm, int weight_round,
-                              const int32_t* global_to_local, int num_local, int32_t* topk_idx, float* topk_w,
-                              int32_t* token_indices, int32_t* expert_offsets, float* route_flat, int* ticket, cudaStream_t st);
 int build_fast(bm_layer* L, const FastPlan& P, cudaStream_t st);
 size_t fast_build_scratch_bytes(const FastPlan& P);
 int launch_arena_decode(const bm_layer* L, int e, int w, int8_t* codes, cudaStream_t st);
@@ -545,16 +542,9 @@ extern "C" int bm_layer_forward(const bm_layer_t* L, const void* x, int x_dtype,
     BM_CUDA(cudaStreamWaitEvent(L->side_stream, L->ev_fork, 0));
     route_stream = L->side_stream;
   }
-  // decode-sized batches: top-k and permutation in one launch (ticket word 6 of the status block); else two or four
-  int rc;
-  if (static_cast<int64_t>(T) * k <= 1024 && num_routed <= 1024 && L->num_experts <= 1024 && k <= 32 && k <= num_routed)
-    rc = launch_route_ticket_fused(logits, logits_dtype, T, num_routed, k, renorm, weight_round, global_to_local, L->num_experts,
-                                   w.topk_idx, w.topk_w, w.token_indices, w.expert_offsets, w.route_flat, L->status_dev + 6,
-                                   static_cast<cudaStream_t>(route_stream));
-  else
-    rc = bm_route(logits, logits_dtype, T, num_routed, k, renorm, weight_round, global_to_local, L->num_experts, TILE_ROWS,
-                  w.topk_idx, w.topk_w, w.token_indices, w.expert_offsets, w.route_flat, /*tile_table=*/nullptr, /*counts=*/nullptr,
-                  w.route_ws, w.route_ws_bytes, route_stream);
+  int rc = bm_route(logits, logits_dtype, T, num_routed, k, renorm, weight_round, global_to_local, L->num_experts, TILE_ROWS,
+                    w.topk_idx, w.topk_w, w.token_indices, w.expert_offsets, w.route_flat, /*tile_table=*/nullptr, /*counts=*/nullptr,
+                    w.route_ws, w.route_ws_bytes, route_stream);
   // the accumulator of the expert stage is cleared off the critical path: by the projection kernel when the
   // skinny one runs, else by a memset beside the routing
   bool zeroed = false;

@@ -270,72 +270,6 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) route_build_fused_kernel(
   write_tile_table(s.scan, E, tile_rows, tile_table, max_tiles, counts, reinterpret_cast<int*>(s.warp_base), s.block_count);
 }
 
-// T*k <= ROUTE_BLOCK, one launch: every block takes ROUTE_WARPS tokens (one warp each) for the top-k, and the block
-// that finishes last (a ticket counter, no waiting) builds the permutation from all blocks' results.  The counter
-// lives in memory that is zero before the first launch; the last block resets it.
-__global__ void __launch_bounds__(ROUTE_BLOCK) route_ticket_fused_kernel(
-    const void* __restrict__ logits, int dtype, int T, int E_routed, int k, int renorm, int weight_round,
-    const int32_t* __restrict__ g2l, int E, int32_t* __restrict__ topk_idx, float* __restrict__ topk_w,
-    int32_t* __restrict__ token_indices, int32_t* __restrict__ expert_offsets, float* __restrict__ route_flat,
-    int* __restrict__ ticket) {
-  extern __shared__ __align__(16) unsigned char sm_raw[];
-  RouteSmem s = carve_route_smem(sm_raw, E);
-  float* prob = reinterpret_cast<float*>(sm_raw + route_smem_bytes_dev(E));   // [ROUTE_WARPS][E_routed], only beyond ROUTE_REG_E
-  __shared__ int is_last;
-  const int warp = threadIdx.x >> 5;
-  const int t = blockIdx.x * ROUTE_WARPS + warp;
-  if (t < T) warp_topk_token(logits, dtype, t, E_routed, k, renorm, weight_round, prob + warp * E_routed, topk_idx, topk_w);
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) is_last = atomicAdd(ticket, 1) == static_cast<int>(gridDim.x) - 1;
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  if (threadIdx.x == 0) *ticket = 0;
-  const int A = T * k;
-  const int i = threadIdx.x;
-  int e = -1;
-  float w = 0.f;
-  if (i < A) {
-    e = __ldcg(topk_idx + i);     // written by other blocks of this launch: read through L2
-    w = __ldcg(topk_w + i);
-    if (g2l) e = g2l[e];
-  }
-  const int rank_w = block_count_and_rank(e, E, s);
-  block_exclusive_scan(s.block_count, s.scan, E);
-  for (int x = threadIdx.x; x <= E; x += blockDim.x) expert_offsets[x] = s.scan[x];
-  if (e >= 0) {
-    const int pos = s.scan[e] + s.warp_base[(threadIdx.x >> 5) * E + e] + rank_w;
-    token_indices[pos] = i / k;
-    route_flat[pos] = w;
-  }
-}
-
-// Routing of a decode-sized batch in one launch, for callers that own a zero-initialised ticket word
-// (bm_layer_forward: the layer's status block).  Returns BM_ERR_UNSUPPORTED when the sizes do not fit.
-int launch_route_ticket_fused(const void* logits, int logits_dtype, int T, int E_routed, int k, int renorm, int weight_round,
-                              const int32_t* global_to_local, int num_local, int32_t* topk_idx, float* topk_w,
-                              int32_t* token_indices, int32_t* expert_offsets, float* route_flat, int* ticket, cudaStream_t st) {
-  const int64_t A = static_cast<int64_t>(T) * k;
-  const size_t smem = route_smem_bytes(num_local > 0 ? num_local : 1) +
-                      (E_routed > ROUTE_REG_E ? sizeof(float) * ROUTE_WARPS * E_routed : 0);
-  BM_REQUIRE(T > 0 && A <= ROUTE_BLOCK && E_routed > 0 && E_routed <= ROUTE_MAX_E && num_local > 0 && num_local <= ROUTE_MAX_E &&
-                 k > 0 && k <= 32 && k <= E_routed && smem <= 200 * 1024 && ticket != nullptr,
-             BM_ERR_UNSUPPORTED, "route: sizes do not fit the single-launch path");
-  BM_REQUIRE(logits && topk_idx && topk_w && token_indices && expert_offsets && route_flat, BM_ERR_INVALID_ARG, "route: null pointer");
-  BM_REQUIRE(logits_dtype >= BM_F16 && logits_dtype <= BM_F32, BM_ERR_INVALID_ARG, "route: bad logits dtype");
-  static bool attr_done = false;
-  if (!attr_done) {
-    BM_CUDA(cudaFuncSetAttribute(route_ticket_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr_done = true;
-  }
-  route_ticket_fused_kernel<<<(T + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_BLOCK, smem, st>>>(
-      logits, logits_dtype, T, E_routed, k, renorm, weight_round, global_to_local, num_local, topk_idx, topk_w, token_indices,
-      expert_offsets, route_flat, ticket);
-  BM_LAUNCH_CHECK("route_ticket_fused_kernel");
-  return BM_OK;
-}
-
 // A > ROUTE_BLOCK: count per block, scan across blocks, scatter.
 __global__ void __launch_bounds__(ROUTE_BLOCK) route_count_kernel(const int32_t* __restrict__ topk_idx,
                                                                  const int32_t* __restrict__ g2l, int A, int E,
