@@ -12,7 +12,7 @@
 //   warp  8     producer: item descriptor, cp.async.bulk of the packed words + scales of (tile, matrix)
 //               sections into a 3-slot ring
 //   warp  9     MMA issue (one thread) and tcgen05.commit to the ring / phase mbarriers
-//   warps 10-17 dequantisers: bit-plane words -> fp16 (q * scale) A-operand stages of 128 rows x 16 K in the
+//   warps 10-17 converters: arena words (nibble / dense 2-bit codes) -> fp16 (q * scale) A-operand stages of 128 rows x 16 K in the
 //               canonical K-major core-matrix layout, 4-stage ring of 4 blocks; they also build the activation operand
 //               act[n, slot] = fp16(h[token, rank(slot)] * s(slot)) once per item
 // Every mbarrier wait is bounded in time and aborts the whole CTA through a shared flag.
