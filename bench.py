@@ -171,9 +171,9 @@ def reference_arm(args):
 
 
 # ------------------------------------------------------------------------------------------- GPU arm
-def timed(fn, steps, stream_sync, use_graph=True):
+def timed(fn, steps, stream_sync, use_graph=True, repeats_out=None):
     """CUDA-event time, in ms, of `steps` calls of fn(i).  The calls are captured once into a CUDA graph
-    (the launch sequence of all `steps` steps) and the graph is replayed inside the timed region, so the
+    (the launch sequence of all `steps` steps), replayed once untimed and then once inside the timed region, so the
     number reflects the device and not the Python interpreter; every launch of the eager sequence is a
     node of the graph."""
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -194,11 +194,22 @@ def timed(fn, steps, stream_sync, use_graph=True):
                 fn(i)
     torch.cuda.current_stream().wait_stream(side)
     stream_sync()
+    graph.replay()      # untimed: the first launch of an instantiated graph also uploads it to the device
+    stream_sync()
     start.record()
     graph.replay()
     stop.record()
     stream_sync()
-    return start.elapsed_time(stop)
+    first = start.elapsed_time(stop)
+    if repeats_out is not None:
+        # further replays of the same graph, each timed on its own: spread of the measurement
+        for _ in range(repeats_out[0]):
+            start.record()
+            graph.replay()
+            stop.record()
+            stream_sync()
+            repeats_out[1].append(start.elapsed_time(stop))
+    return first
 
 
 def active_expert_bytes(packed, offsets_cpu):
@@ -255,7 +266,7 @@ def gpu_arm(args):
     pk = peaks()
     L = args.layers
     use_ep = world > 1 and args.parallel == "ep"
-    if use_ep:
+    if world > 1:
         from bitsmoe_b200 import ep
 
         class _EpAdapter:
@@ -268,11 +279,12 @@ def gpu_arm(args):
                 self.packed = self.epl.packed
 
             def forward(self, x, logits, top_k, renorm, wdt, out=None, path=0):
-                y = self.epl.forward(x, logits, wdt)
+                y = self.epl.forward(x, logits, wdt, uniform=True)
                 if out is not None:
                     out.copy_(y)
                 return y
 
+    if use_ep:
         # every rank generates the same weight sets (same seeds) and keeps only its experts
         layers = [_EpAdapter(synth.make_layer(cfg, seed=42 + i, device=dev)) for i in range(L)]
     else:
@@ -294,8 +306,12 @@ def gpu_arm(args):
         for i in range(max(warmup, 3)):
             step(i)
         barrier()
-        ms = timed(step, steps, sync, use_graph=True)
+        reps = (8, [])
+        ms = timed(step, steps, sync, use_graph=True, repeats_out=reps if want_roofline else None)
         out = {"tokens": T, "ms_per_step": ms / steps, "tokens_per_s": T * steps / (ms * 1e-3)}
+        if reps[1]:
+            r = sorted(x / steps for x in reps[1])
+            out["ms_per_step_replays"] = {"n": len(r), "p10": r[max(0, int(0.1 * len(r)) )], "p50": r[len(r) // 2], "p90": r[min(len(r) - 1, int(0.9 * len(r)))]}
         if want_roofline and use_ep:
             out.update(experts_kernel_ms=None, experts_bytes=None, active_experts=None)
         elif want_roofline:
@@ -327,7 +343,7 @@ def gpu_arm(args):
         result is copied back inside the timed region.  The copies run on their own streams with two sets of
         device buffers, so step i+1's upload and step i-1's download overlap step i's kernels, as a serving loop
         would arrange them; the whole pipeline is one CUDA graph."""
-        NB = 2
+        NB = int(os.environ.get("BM_E2E_BUFFERS", "2"))
         hx = [synth.activations(cfg, T, seed=70 + i + 1000 * rank).pin_memory() for i in range(4)]
         hl = [synth.router_logits(cfg, T, seed=90 + i + 1000 * rank).pin_memory() for i in range(4)]
         hy = [torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(NB)]
@@ -369,7 +385,7 @@ def gpu_arm(args):
         ms = timed(lambda _i: pipeline(steps), 1, sync, use_graph=True)
         return {"value": T * steps / (ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": dx[0].numel() * 2 + dl[0].numel() * 4,
                 "d2h_bytes_per_step": dy[0].numel() * 2,
-                "overlap": "uploads and downloads on their own streams, two device buffer sets, one CUDA graph"}
+                "overlap": f"uploads and downloads on their own streams, {NB} device buffer sets, one CUDA graph"}
 
     with ClockSampler(local) as clk:
         head = decode_case(args.tokens, args.steps, args.warmup, True)
@@ -396,6 +412,39 @@ def gpu_arm(args):
                                       "frac_of_bf16_peak": flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], "router": "zipf 1.1"}
         except Exception as ex:  # keep the headline if the large case fails
             extra["prefill_error"] = repr(ex)
+
+    if world > 1 and not use_ep and not args.no_extras:
+        # the same layer expert-parallel (experts sharded over the ranks, rank-space exchange over NCCL): both steps
+        # in CUDA graphs (fixed-size all_gather / reduce_scatter exchange); max over ranks
+        import torch.distributed as dist
+        try:
+            ep_layers = [_EpAdapter(synth.make_layer(cfg, seed=42 + i, device=dev)) for i in range(min(L, 4))]
+            Le = len(ep_layers)
+            T = args.tokens
+            xs = [synth.activations(cfg, T, seed=7 + i + 1000 * rank, device=dev) for i in range(Le)]
+            lg = [synth.router_logits(cfg, T, seed=9 + i + 1000 * rank, device=dev) for i in range(Le)]
+            estep = lambda i: ep_layers[i % Le].forward(xs[i % Le], lg[i % Le], cfg.top_k, True, torch.bfloat16)
+            for i in range(3):
+                estep(i)
+            barrier()
+            n = min(args.steps, 50)
+            ems = timed(estep, n, sync, use_graph=True) / n
+            Tp = args.prefill_tokens
+            xp = synth.activations(cfg, Tp, seed=3 + 1000 * rank, device=dev)
+            lp = synth.router_logits(cfg, Tp, seed=4 + 1000 * rank, device=dev)     # N(0,1): near-uniform expert load
+            pstep = lambda i: ep_layers[i % Le].forward(xp, lp, cfg.top_k, True, torch.bfloat16)
+            for i in range(2):
+                pstep(i)
+            barrier()
+            pms = timed(pstep, 3, sync, use_graph=True) / 3
+            t = torch.tensor([ems, pms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            extra["ep_decode"] = {"tokens_per_gpu": T, "ms_per_step": float(t[0]), "tokens_per_s": world * T / (float(t[0]) * 1e-3)}
+            extra["ep_prefill"] = {"tokens_per_gpu": Tp, "ms_per_step": float(t[1]), "tokens_per_s": world * Tp / (float(t[1]) * 1e-3),
+                                   "router": "N(0,1) logits"}
+            del ep_layers
+        except Exception as ex:
+            extra["ep_error"] = repr(ex)
 
     value = head["tokens_per_s"]
     ms_step = head["ms_per_step"]
@@ -438,6 +487,8 @@ def gpu_arm(args):
                      "algorithmic_bytes": head["experts_bytes"], "active_experts": head["active_experts"]},
         "extra": extra,
     }
+    if "ms_per_step_replays" in head:
+        line["ms_per_step_replays"] = head["ms_per_step_replays"]
     if not args.no_extras and world == 1:
         cpu_layer = synth.make_layer(cfg, seed=42, device=dev)
         cpu_layer.tables = {t: {f: [x.cpu() for x in v] for f, v in fl.items()} for t, fl in cpu_layer.tables.items()}

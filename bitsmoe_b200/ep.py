@@ -167,12 +167,15 @@ class ExpertParallelPackedLayer:
         self.gather_ep = GatherExpertParallel(num_experts, top_k, build, self.packed.experts_forward, group,
                                               device=self.packed.device)
         self.gather_max_tokens = 256
+        # with `uniform=True` (the caller guarantees one token count on all ranks) the gather exchange is used up to
+        # this many tokens per rank; it moves G*T rows per rank but needs no host read and no sorting
+        self.gather_max_tokens_uniform = 131072 // world
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, weight_dtype=torch.float16,
-                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                residual: Optional[torch.Tensor] = None, uniform: bool = False) -> torch.Tensor:
         from .layer import route_topk
         idx, w = route_topk(logits, self.top_k, self.norm_topk_prob, weight_dtype)
-        if x.shape[0] <= self.gather_max_tokens:
+        if x.shape[0] <= (self.gather_max_tokens_uniform if uniform else self.gather_max_tokens):
             # decode-sized batch: fixed-size exchanges, nothing read back to the host (CUDA-graph capturable);
             # every rank must take this branch together, i.e. use the same token count per rank
             pair = torch.empty((2, x.shape[0], self.packed.rank_in), dtype=torch.float16, device=x.device)
@@ -252,9 +255,11 @@ class GatherExpertParallel:
         # of the up block view (which starts T rows later)
         tok_v = (torch.div(tok, T, rounding_mode="floor") * (2 * T) + tok % T).to(torch.int32)
         flat = h_all.view(G * 2 * T, r)
-        part = self.experts_fn(flat, flat[T:], tok_v, off, rw)                # [rows >= G*2T - T, rank_out]
-        part = part[: G * 2 * T - T] if part.shape[0] > G * 2 * T - T else part
-        full = torch.zeros((G * 2 * T, rank_out), dtype=torch.float32, device=h_pair.device)
-        full[: part.shape[0]] = part
-        mine = full.view(G, 2, T, rank_out)[:, 0].contiguous()                # [G, T, rank_out]
+        part = self.experts_fn(flat, flat[T:], tok_v, off, rw)                # one row per row of `flat` (or T fewer)
+        if part.shape[0] == G * 2 * T:
+            mine = part.view(G, 2, T, rank_out)[:, 0].contiguous()            # [G, T, rank_out]: the gate-block rows
+        else:
+            full = torch.zeros((G * 2 * T, rank_out), dtype=torch.float32, device=h_pair.device)
+            full[: part.shape[0]] = part
+            mine = full.view(G, 2, T, rank_out)[:, 0].contiguous()
         return _reduce_scatter_rows(mine, self.group)
