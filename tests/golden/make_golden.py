@@ -2,7 +2,7 @@
 that has the reference tree; the fixtures it writes are committed, the tree is
 not needed afterwards.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <BitsMoE checkout>]
 
 What is taken from the reference (imported, executed on the CPU, unmodified):
   bitsmoe.quant.quantizer.quantize_symmetric
