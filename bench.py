@@ -340,10 +340,12 @@ def gpu_arm(args):
 
     def e2e_case(T, steps, warmup):
         """Host buffers in, host buffer out, every step: the step's inputs are copied from pinned memory and its
-        result is copied back inside the timed region.  The copies run on their own streams with two sets of
-        device buffers, so step i+1's upload and step i-1's download overlap step i's kernels, as a serving loop
-        would arrange them; the whole pipeline is one CUDA graph."""
-        NB = int(os.environ.get("BM_E2E_BUFFERS", "2"))
+        result is copied back inside the timed region.  The copies run on their own streams, so that uploads and
+        downloads overlap other steps' kernels as a serving loop would arrange them; steps are handed from stream
+        to stream in groups of GROUP (two groups of device buffer sets), because every cross-stream edge of the
+        CUDA graph costs a few microseconds.  The whole pipeline is one CUDA graph."""
+        GROUP = int(os.environ.get("BM_E2E_GROUP", "4"))
+        NB = 2 * GROUP
         hx = [synth.activations(cfg, T, seed=70 + i + 1000 * rank).pin_memory() for i in range(4)]
         hl = [synth.router_logits(cfg, T, seed=90 + i + 1000 * rank).pin_memory() for i in range(4)]
         hy = [torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(NB)]
@@ -354,29 +356,33 @@ def gpu_arm(args):
 
         def pipeline(n):
             comp = torch.cuda.current_stream(dev)
-            ev_c, ev_out = [None] * n, [None] * n
+            ngroups = (n + GROUP - 1) // GROUP
+            ev_c, ev_out = [None] * ngroups, [None] * ngroups
             s_in.wait_stream(comp)
             s_out.wait_stream(comp)
-            for i in range(n):
-                b = i % NB
+            for gidx in range(ngroups):
+                lo, hi = gidx * GROUP, min(n, (gidx + 1) * GROUP)
                 with torch.cuda.stream(s_in):
-                    if i >= NB:
-                        s_in.wait_event(ev_c[i - NB])        # the kernels that read this buffer set are done
-                    dx[b].copy_(hx[i % 4], non_blocking=True)
-                    dl[b].copy_(hl[i % 4], non_blocking=True)
+                    if gidx >= 2:
+                        s_in.wait_event(ev_c[gidx - 2])       # the kernels that read these buffer sets are done
+                    for i in range(lo, hi):
+                        dx[i % NB].copy_(hx[i % 4], non_blocking=True)
+                        dl[i % NB].copy_(hl[i % 4], non_blocking=True)
                     ev_in = torch.cuda.Event()
                     ev_in.record(s_in)
                 comp.wait_event(ev_in)
-                if i >= NB:
-                    comp.wait_event(ev_out[i - NB])          # the previous result in this buffer set has left
-                layers[i % L].forward(dx[b], dl[b], cfg.top_k, True, torch.bfloat16, out=dy[b], path=args.path)
-                ev_c[i] = torch.cuda.Event()
-                ev_c[i].record(comp)
+                if gidx >= 2:
+                    comp.wait_event(ev_out[gidx - 2])         # the previous results in these buffer sets have left
+                for i in range(lo, hi):
+                    layers[i % L].forward(dx[i % NB], dl[i % NB], cfg.top_k, True, torch.bfloat16, out=dy[i % NB], path=args.path)
+                ev_c[gidx] = torch.cuda.Event()
+                ev_c[gidx].record(comp)
                 with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_c[i])
-                    hy[b].copy_(dy[b], non_blocking=True)
-                    ev_out[i] = torch.cuda.Event()
-                    ev_out[i].record(s_out)
+                    s_out.wait_event(ev_c[gidx])
+                    for i in range(lo, hi):
+                        hy[i % NB].copy_(dy[i % NB], non_blocking=True)
+                    ev_out[gidx] = torch.cuda.Event()
+                    ev_out[gidx].record(s_out)
             comp.wait_stream(s_in)
             comp.wait_stream(s_out)
 
@@ -385,7 +391,8 @@ def gpu_arm(args):
         ms = timed(lambda _i: pipeline(steps), 1, sync, use_graph=True)
         return {"value": T * steps / (ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": dx[0].numel() * 2 + dl[0].numel() * 4,
                 "d2h_bytes_per_step": dy[0].numel() * 2,
-                "overlap": f"uploads and downloads on their own streams, {NB} device buffer sets, one CUDA graph"}
+                "overlap": f"uploads and downloads on their own streams, handed over in groups of {GROUP} steps, {NB} device "
+                           "buffer sets, one CUDA graph"}
 
     with ClockSampler(local) as clk:
         head = decode_case(args.tokens, args.steps, args.warmup, True)
