@@ -99,9 +99,6 @@ struct FastPlan {
   size_t units_off = 0;
   size_t total = 0;
   int max_unit_bytes = 0, max_slots = 0, max_words = 0;
-  int* status_dev = nullptr;       // device flag set by a kernel whose bounded wait gave up
-  cudaStream_t side_stream = nullptr;   // routing runs here, beside the basis projection
-  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
 __host__ __device__ inline int words_per_row(int bits) { return bits == 16 ? 16 : bits; }
