@@ -543,6 +543,13 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
   if (threadIdx.x == 0 && abort_flag_s) atomicExch(status, BM_ERR_TIMEOUT);
 }
 
+// Whether the layer's largest expert fits the tensor path's shared- and tensor-memory budget (AUTO falls back to the
+// decode path otherwise).
+bool experts_tc_fits(const bm_layer* L) {
+  return L->num_experts <= XT_MAX_E && L->intermediate % N_TILE == 0 && L->max_slots <= 3 * 128 &&
+         xt_smem_bytes(L->max_slots, L->max_words, L->num_experts) <= 224 * 1024;
+}
+
 int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                       const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st) {
   BM_REQUIRE(L->num_experts <= XT_MAX_E, BM_ERR_UNSUPPORTED, "experts_tc: more than %d experts", XT_MAX_E);

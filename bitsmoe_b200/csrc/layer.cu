@@ -53,6 +53,7 @@ size_t fast_build_scratch_bytes(const FastPlan& P);
 int launch_arena_decode(const bm_layer* L, int e, int w, int8_t* codes, cudaStream_t st);
 int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                           const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
+bool experts_tc_fits(const bm_layer* L);
 int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                       const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
 int launch_experts_generic(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
@@ -456,7 +457,7 @@ static int experts_forward_impl(const bm_layer_t* L, const uint16_t* h_gate, con
              "experts_forward: null pointer");
   BM_REQUIRE(path != BM_PATH_TENSOR || L->fast_ok, BM_ERR_UNSUPPORTED,
              "experts_forward: the tensor path needs 1- to 4-bit rows and full tiles; this layer has neither");
-  if (L->fast_ok && (path == BM_PATH_TENSOR || (path == BM_PATH_AUTO && num_assign > 16 * L->num_experts && !getenv("BM_NO_TC"))))
+  if (L->fast_ok && (path == BM_PATH_TENSOR || (path == BM_PATH_AUTO && num_assign > 16 * L->num_experts && experts_tc_fits(L) && !getenv("BM_NO_TC"))))
     return launch_experts_tc(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up), token_indices,
                              expert_offsets, route_weights, T, rank_accum, st);
   BM_REQUIRE(path != BM_PATH_DECODE || L->fast_ok, BM_ERR_UNSUPPORTED,

@@ -347,3 +347,41 @@ def test_one_to_four_bit_rows_on_fast_paths(low_bits, T, path):
     helpers.assert_close(got, o["rank_accum"], rtol=1e-2, atol=3e-4, what="rank_accum (1-4 bit rows) vs fp32 oracle")
     gen = packed.experts_forward(*args, path=capi.PATH_GENERIC)
     helpers.assert_close(got, gen, rtol=1e-2, atol=3e-4, what="fast path vs generic path, 1-4 bit rows")
+
+
+_SWEEP = [
+    # (hidden, experts, intermediate, top_k, rank, bit_probs)
+    (256, 4, 128, 2, 32, ((2, 1.0),)),
+    (384, 6, 256, 3, 48, ((4, 1.0),)),
+    (512, 12, 640, 4, 96, ((1, 0.5), (3, 0.5))),
+    (256, 5, 384, 1, 200, ((2, 0.6), (3, 0.3), (4, 0.1))),
+    (1024, 24, 256, 6, 320, ((2, 0.9), (4, 0.1))),
+]
+
+
+@pytest.mark.parametrize("case", range(len(_SWEEP)))
+def test_fast_paths_shape_sweep(case):
+    """Odd ranks, group sizes that need padding, single-width layers, top-1 routing: decode and tensor paths against
+    the fp32 oracle and the generic path."""
+    hidden, E, I, k, r, probs = _SWEEP[case]
+    cfg = synth.LayerConfig(f"sweep-{case}", hidden, E, I, k, rank=r, bit_probs=probs)
+    layer = synth.make_layer(cfg, seed=100 + case, device=DEV)
+    packed = synth.to_packed_layer(layer, DEV)
+    assert packed.has_fast_layout or r > 256      # very wide ranks may exceed the shared-memory budget of the arena paths
+    experts = helpers.decoded_experts(layer)
+    for T in (1, 9, 70):
+        x, logits = _inputs(layer, T, 500 + 10 * case + T)
+        o = oforward.layer_forward(x, logits, layer.vh_gate.cpu(), layer.vh_up.cpu(), layer.u_down.cpu(), experts, cfg.top_k)
+        args = [o[kk].to(DEV) for kk in ("h_gate", "h_up", "token_indices", "expert_offsets", "route_flat")]
+        gen = packed.experts_forward(*args, path=capi.PATH_GENERIC)
+        helpers.assert_close(gen, o["rank_accum"], rtol=1e-3, atol=1e-5, what=f"sweep {case} T={T} generic vs oracle")
+        paths = (capi.PATH_DECODE, capi.PATH_TENSOR) if packed.has_fast_layout else ()
+        if r > 256:
+            paths = paths[:1] + (capi.PATH_AUTO,)      # the tensor path's shared-memory budget ends near rank 288: AUTO must cope
+        for path in paths:
+            got = packed.experts_forward(*args, path=path)
+            packed.check_status()
+            helpers.assert_close(got, o["rank_accum"], rtol=1e-2, atol=3e-4, what=f"sweep {case} T={T} path={path} vs oracle")
+            helpers.assert_close(got, gen, rtol=1e-2, atol=3e-4, what=f"sweep {case} T={T} path={path} vs generic")
+        y = packed.forward(x.to(DEV), logits.to(DEV), cfg.top_k, True, torch.bfloat16)
+        helpers.assert_close(y, o["y_fp32"], what=f"sweep {case} T={T} layer output")
