@@ -69,59 +69,63 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmTcArgs a) {
   // lane -> (row within an 8-row group, one of 4 chunks): a quarter warp fills one 128-byte core matrix
   const int r8 = lane & 7, kq = lane >> 3;
 
-  auto issue_slice = [&](int s) {
-    const int buf = s % TC_STAGES;
-    unsigned char* As = tc_smem + buf * TC_STAGE_BYTES;
-    unsigned char* Bs = As + TC_A_BYTES;
+  constexpr int AV = (TC_BM / 8 * 2) / (TC_THREADS / 32);   // 16-byte vectors of the A slice per thread
+  // A operand, fp16 activations: straight to shared memory
+  auto issue_a_async = [&](int s) {
+    unsigned char* As = tc_smem + (s % TC_STAGES) * TC_STAGE_BYTES;
     const int k0 = s * TC_BK;
-    if (XD == BM_F16) {
-      const uint16_t* X = reinterpret_cast<const uint16_t*>(a.X);
+    const uint16_t* X = reinterpret_cast<const uint16_t*>(a.X);
 #pragma unroll
-      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
-        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
-        const bool valid = m0 + r < a.M;
-        cp_async16(As + canon_off(TC_BM, r, kc), X + static_cast<size_t>(valid ? m0 + r : 0) * a.K + k0 + kc * 8, valid);
-      }
-    } else if (XD == BM_BF16) {
-      const uint16_t* X = reinterpret_cast<const uint16_t*>(a.X);
-      uint4 raw[(TC_BM / 8 * 2) / (TC_THREADS / 32)];
+    for (int i = 0; i < AV; ++i) {
+      const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+      const bool valid = m0 + r < a.M;
+      cp_async16(As + canon_off(TC_BM, r, kc), X + static_cast<size_t>(valid ? m0 + r : 0) * a.K + k0 + kc * 8, valid);
+    }
+  };
+  // A operand, bf16 / fp32 activations: loaded to registers one slice ahead of the slice being stored, so that the
+  // load latency overlaps a whole loop iteration; rounded to fp16 on the way to shared memory
+  uint4 raw[AV][XD == BM_F32 ? 2 : 1];
+  auto load_a_regs = [&](int s) {
+    const int k0 = s * TC_BK;
 #pragma unroll
-      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
-        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
-        raw[i] = make_uint4(0, 0, 0, 0);
-        if (m0 + r < a.M) raw[i] = *reinterpret_cast<const uint4*>(X + static_cast<size_t>(m0 + r) * a.K + k0 + kc * 8);
-      }
-#pragma unroll
-      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
-        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
-        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-        __half2 h[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xffff0000u));
-        *reinterpret_cast<uint4*>(As + canon_off(TC_BM, r, kc)) = *reinterpret_cast<uint4*>(h);
-      }
-    } else {
-      const float* X = reinterpret_cast<const float*>(a.X);
-      float4 f[(TC_BM / 8 * 2) / (TC_THREADS / 32)][2];
-#pragma unroll
-      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
-        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
-        if (m0 + r < a.M) {
-          const float* src = X + static_cast<size_t>(m0 + r) * a.K + k0 + kc * 8;
-          f[i][0] = *reinterpret_cast<const float4*>(src);
-          f[i][1] = *reinterpret_cast<const float4*>(src + 4);
+    for (int i = 0; i < AV; ++i) {
+      const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+      raw[i][0] = make_uint4(0, 0, 0, 0);
+      if (XD == BM_F32) raw[i][XD == BM_F32 ? 1 : 0] = make_uint4(0, 0, 0, 0);
+      if (m0 + r < a.M) {
+        if (XD == BM_BF16) {
+          raw[i][0] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.X) + static_cast<size_t>(m0 + r) * a.K + k0 + kc * 8);
         } else {
-          f[i][0] = f[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float* src = reinterpret_cast<const float*>(a.X) + static_cast<size_t>(m0 + r) * a.K + k0 + kc * 8;
+          raw[i][0] = *reinterpret_cast<const uint4*>(src);
+          raw[i][XD == BM_F32 ? 1 : 0] = *reinterpret_cast<const uint4*>(src + 4);
         }
       }
-#pragma unroll
-      for (int i = 0; i < (TC_BM / 8 * 2) / (TC_THREADS / 32); ++i) {
-        const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
-        __half2 h[4] = {__floats2half2_rn(f[i][0].x, f[i][0].y), __floats2half2_rn(f[i][0].z, f[i][0].w),
-                        __floats2half2_rn(f[i][1].x, f[i][1].y), __floats2half2_rn(f[i][1].z, f[i][1].w)};
-        *reinterpret_cast<uint4*>(As + canon_off(TC_BM, r, kc)) = *reinterpret_cast<uint4*>(h);
-      }
     }
+  };
+  auto store_a_regs = [&](int s) {
+    unsigned char* As = tc_smem + (s % TC_STAGES) * TC_STAGE_BYTES;
+#pragma unroll
+    for (int i = 0; i < AV; ++i) {
+      const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
+      __half2 h[4];
+      if (XD == BM_BF16) {
+        const uint32_t w[4] = {raw[i][0].x, raw[i][0].y, raw[i][0].z, raw[i][0].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xffff0000u));
+      } else {
+        const uint4 lo = raw[i][0], hi = raw[i][XD == BM_F32 ? 1 : 0];
+        h[0] = __floats2half2_rn(__uint_as_float(lo.x), __uint_as_float(lo.y));
+        h[1] = __floats2half2_rn(__uint_as_float(lo.z), __uint_as_float(lo.w));
+        h[2] = __floats2half2_rn(__uint_as_float(hi.x), __uint_as_float(hi.y));
+        h[3] = __floats2half2_rn(__uint_as_float(hi.z), __uint_as_float(hi.w));
+      }
+      *reinterpret_cast<uint4*>(As + canon_off(TC_BM, r, kc)) = *reinterpret_cast<uint4*>(h);
+    }
+  };
+  auto issue_b = [&](int s) {
+    unsigned char* Bs = tc_smem + (s % TC_STAGES) * TC_STAGE_BYTES + TC_A_BYTES;
+    const int k0 = s * TC_BK;
 #pragma unroll
     for (int i = 0; i < (TC_BN / 8 * 2) / (TC_THREADS / 32); ++i) {
       const int v = warp + i * (TC_THREADS / 32), grp = v >> 1, kc = (v & 1) * 4 + kq, r = grp * 8 + r8;
@@ -131,9 +135,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmTcArgs a) {
   };
 
   for (int s = 0; s < TC_AHEAD; ++s) {
-    if (s < nslices) issue_slice(s);
+    if (s < nslices) {
+      if (XD == BM_F16) issue_a_async(s);
+      else { load_a_regs(s); store_a_regs(s); }
+      issue_b(s);
+    }
     cp_async_commit();
   }
+  if (XD != BM_F16 && TC_AHEAD < nslices) load_a_regs(TC_AHEAD);
   for (int s = 0; s < nslices; ++s) {
     const int buf = s % TC_STAGES;
     cp_async_wait<TC_AHEAD - 1>();     // this thread's copies of slice s have landed
@@ -155,7 +164,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmTcArgs a) {
     if (nxt < nslices && ok) {
       // stage nxt % STAGES was last read by the MMAs of slice nxt - STAGES = s - 1
       if (nxt >= TC_STAGES && !tc::mbar_wait(&bar_free[nxt % TC_STAGES], ((nxt / TC_STAGES) - 1) & 1)) ok = false;
-      if (ok) issue_slice(nxt);
+      if (ok) {
+        if (XD == BM_F16) issue_a_async(nxt);
+        else {
+          store_a_regs(nxt);                               // loaded during the previous iteration
+          if (nxt + 1 < nslices) load_a_regs(nxt + 1);
+        }
+        issue_b(nxt);
+      }
     }
     cp_async_commit();
   }
