@@ -57,13 +57,10 @@ void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P) {
     int o = 0;
     for (int w = 0; w < 3; ++w) { fe.sec_off[w] = o; o += fe.m[w].nslots * 2; }       // multiples of 32 bytes
     for (int w = 0; w < 3; ++w) { fe.sec_off[3 + w] = o; o += fe.m[w].words * 4; }   // multiples of 512 bytes
-    fe.stage_bytes = static_cast<int32_t>(align_up(o, 128));
-    // second copy of the codes, one word (or two) per operand row and 16-block of the contraction
-    for (int w = 0; w < 3; ++w) { fe.rm_off[w] = o; o += fe.m[w].words * 4; }
     fe.unit_bytes = static_cast<int32_t>(align_up(o, 128));
     fe.unit_base = static_cast<int64_t>(off);
     off += static_cast<size_t>(fe.unit_bytes) * L->n_tiles;
-    if (fe.stage_bytes > P->max_unit_bytes) P->max_unit_bytes = fe.stage_bytes;
+    if (fe.unit_bytes > P->max_unit_bytes) P->max_unit_bytes = fe.unit_bytes;
   }
   P->total = align_up(off, 256);
   // a unit block plus activation staging has to fit one CTA's shared memory
@@ -184,47 +181,6 @@ __global__ void __launch_bounds__(256) repack_words_kernel(const ExpertDev* __re
   }
 }
 
-// grid (E, n_tiles, 3): one thread per word of the row-major copy.
-__global__ void __launch_bounds__(256) repack_rm_words_kernel(const ExpertDev* __restrict__ experts,
-                                                             const FastExpert* __restrict__ fast,
-                                                             const int16_t* __restrict__ slot_row_all,
-                                                             const int32_t* __restrict__ slot_row_off,
-                                                             unsigned char* __restrict__ arena) {
-  const int e = blockIdx.x, tile = blockIdx.y, w = blockIdx.z;
-  const MatDev& md = experts[e].m[w];
-  const FastExpert& fe = fast[e];
-  const FastMat& fm = fe.m[w];
-  const int16_t* slot_row = slot_row_all + slot_row_off[e * 3 + w];
-  uint32_t* out = reinterpret_cast<uint32_t*>(arena + fe.unit_base + static_cast<int64_t>(tile) * fe.unit_bytes + fe.rm_off[w]);
-  const int nib_words = fm.nblk[0] * 256, n0 = fm.nblk[0] * 16, n1 = fm.nblk[1] * 16;
-  for (int i = threadIdx.x; i < fm.words; i += blockDim.x) {
-    const bool dense = i >= nib_words;
-    int kb, row, half = 0;            // kb: 16-block of the contraction; row: operand row
-    if (!dense) {
-      half = i & 1;
-      const int j = i >> 1;
-      if (w < 2) { kb = j / 128; row = j % 128; }
-      else { kb = j / n0; row = j % n0; }
-    } else {
-      const int j = i - nib_words;
-      if (w < 2) { kb = fm.nblk[0] + j / 128; row = j % 128; }
-      else { kb = j / n1; row = n0 + j % n1; }
-    }
-    uint32_t word = 0;
-    for (int kk = 0; kk < (dense ? 16 : 8); ++kk) {
-      const int k = dense ? kk : 8 * half + kk;
-      int slot, col;
-      if (w < 2) { slot = kb * 16 + k; col = row; }          // contraction = slots, operand row = column of the tile
-      else { slot = row; col = kb * 16 + k; }                // contraction = columns, operand row = slot
-      const int srow = slot_row[slot];
-      const int code = srow >= 0 ? source_q(md, srow, col, tile) : 0;
-      if (dense) word |= static_cast<uint32_t>((code + FAST_DENSE_OFFSET) & 3) << rm_dense_shift(k);
-      else word |= static_cast<uint32_t>((code + FAST_NIB_OFFSET) & 15) << rm_nib_shift(kk);
-    }
-    out[i] = word;
-  }
-}
-
 // int8 codes [n_rows, intermediate] read back from the arena words: one thread per (slot, column).
 __global__ void __launch_bounds__(256) arena_decode_kernel(const FastExpert* __restrict__ fast, int e, int w, int n_tiles,
                                                           int intermediate, const unsigned char* __restrict__ arena,
@@ -280,8 +236,6 @@ int build_fast(bm_layer* L, const FastPlan& P, cudaStream_t st) {
   BM_LAUNCH_CHECK("repack_tables_kernel");
   repack_words_kernel<<<grid, 256, 0, st>>>(L->experts_dev, d_fast, d_rows, d_offs, arena);
   BM_LAUNCH_CHECK("repack_words_kernel");
-  repack_rm_words_kernel<<<grid, 256, 0, st>>>(L->experts_dev, d_fast, d_rows, d_offs, arena);
-  BM_LAUNCH_CHECK("repack_rm_words_kernel");
   BM_CUDA(cudaStreamSynchronize(st));
   return BM_OK;
 }

@@ -86,9 +86,7 @@ struct FastExpert {
   int64_t unit_base;    // byte offset of tile 0's unit block from arena base
   int32_t unit_bytes;   // bytes per unit block (multiple of 128)
   int32_t sec_off[6];   // byte offsets inside a unit: scale g,u,d then words g,u,d
-  int32_t rm_off[3];    // byte offsets inside a unit of the row-major word sections g,u,d (see fast_layout.cuh)
-  int32_t stage_bytes;  // bytes a kernel stages per unit: scales + one set of word sections
-  int32_t pad_[3];
+  int32_t pad_;
 };
 
 struct FastPlan {

@@ -58,14 +58,4 @@ __host__ __device__ inline int slot_pos(int slot) { return (slot & ~31) + pos32(
 __host__ __device__ inline int nib_shift(int hi8, int k) { return 16 * (k & 1) + 4 * ((k >> 3) * 2 + hi8); }
 __host__ __device__ inline int dense_shift(int blk, int hi8, int k) { return 16 * (k & 1) + 8 * blk + 4 * hi8 + 2 * (k >> 3); }
 
-// Row-major copy of the same codes (for operand rows written to tensor memory one thread per row): a word belongs to
-// one operand row and one 16-block of the contraction.
-//   nibble group: two words per (row, block); word h holds k = 8h .. 8h+7, even k = 8h+2j at nibble j, odd at nibble j+4
-//   dense group:  one word per (row, block); even k = 2j at 2-bit field j, odd k = 2j+1 at field 8+j
-// so ((w >> 4j) & 0x000F000F) resp. ((w >> 2j) & 0x00030003) is the pair (k even, k odd) of output register j.
-// gate / up: rows = the tile's 128 columns;  nibble words [block][row][2], then dense words [block][row]
-// down:      rows = slots;                   nibble words [column block][nibble slot][2], then dense [column block][dense slot]
-__host__ __device__ inline int rm_nib_shift(int k8) { return 4 * (k8 >> 1) + 16 * (k8 & 1); }      // k8 = k & 7
-__host__ __device__ inline int rm_dense_shift(int k) { return 2 * (k >> 1) + 16 * (k & 1); }
-
 }  // namespace bm

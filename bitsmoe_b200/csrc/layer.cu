@@ -54,9 +54,6 @@ int launch_arena_decode(const bm_layer* L, int e, int w, int8_t* codes, cudaStre
 int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                           const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
 bool experts_tc_fits(const bm_layer* L);
-int launch_experts_decode_tm(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
-                             const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
-bool experts_decode_tm_fits(const bm_layer* L);
 int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                       const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
 int launch_experts_generic(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
@@ -465,9 +462,6 @@ static int experts_forward_impl(const bm_layer_t* L, const uint16_t* h_gate, con
                              expert_offsets, route_weights, T, rank_accum, st);
   BM_REQUIRE(path != BM_PATH_DECODE || L->fast_ok, BM_ERR_UNSUPPORTED,
              "experts_forward: the decode path needs 1- to 4-bit rows and full tiles; this layer has neither");
-  if (L->fast_ok && path != BM_PATH_GENERIC && getenv("BM_DECODE_TM") && experts_decode_tm_fits(L))
-    return launch_experts_decode_tm(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
-                                    token_indices, expert_offsets, route_weights, T, rank_accum, st);
   if (L->fast_ok && path != BM_PATH_GENERIC)
     return launch_experts_decode(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
                                  token_indices, expert_offsets, route_weights, T, rank_accum, st);
