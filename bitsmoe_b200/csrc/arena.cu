@@ -32,6 +32,23 @@ void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P) {
       P->slot_row_off[e * 3 + w] = static_cast<int32_t>(P->slot_row.size());
       // gate / up contract over the slots in pairs of 16-blocks; down only needs whole 16-row blocks
       const int gran = w < 2 ? 32 : 16;
+      // A 1- or 2-bit row also fits a nibble slot (q + 8 is in [6, 9]).  Moving m of them over can empty padding on
+      // both sides: take the m that minimises words (a nibble block is 256 words, a dense one 128) plus 128 per
+      // 16-block (= per MMA column block), the smallest such m.
+      {
+        const int n0 = static_cast<int>(rows[0].size()), n1 = static_cast<int>(rows[1].size());
+        long best_cost = -1;
+        int best_m = 0;
+        for (int m = 0; m <= n1; ++m) {
+          const int p0 = (n0 + m + gran - 1) / gran * gran, p1 = (n1 - m + gran - 1) / gran * gran;
+          const long cost = 16L * p0 + 8L * p1 + 128L * ((p0 + p1) / 16);
+          if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_m = m; }
+        }
+        for (int i = 0; i < best_m; ++i) {
+          rows[0].push_back(rows[1].back());
+          rows[1].pop_back();
+        }
+      }
       int total_blk = 0;
       for (int g = 0; g < 2; ++g) {
         const int padded = (static_cast<int>(rows[g].size()) + gran - 1) / gran * gran;

@@ -11,7 +11,8 @@
 // in which a 32-bit word is the property of ONE thread of an m16n8k16 MMA (lane = 4 g + t) and
 // expands into A-fragment registers with one mask (and at most one shift) per register:
 //
-//   nibble group (3- and 4-bit rows; stored code u = q + 8, one word = one 16x16 block):
+//   nibble group (3- and 4-bit rows, plus the 1- and 2-bit rows that would only fill padding of the dense
+//   group: see plan_fast; stored code u = q + 8, one word = one 16x16 block):
 //     nibble i of the lower half-word, i = 0..3 : (row g, k 2t) (row g+8, k 2t) (row g, k 2t+8) (row g+8, k 2t+8)
 //     same nibble of the upper half-word        : the neighbour k + 1
 //     a0 = w & 0x000F000F, a1 = w & 0x00F000F0, a2 = (w >> 8) & 0x000F000F, a3 = (w >> 8) & 0x00F000F0
