@@ -488,7 +488,7 @@ def gpu_arm(args):
                      "frac": (achieved / pk["hbm_gbs"]) if achieved else None,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this workload, from the ncu capture
                      # summarised in profiles/experts_decode_kernel_qwen3-30b_64tok.md
-                     "traffic": 27221760 if (args.tokens == 64 and args.path == 0 and achieved) else None,
+                     "traffic": 25056512 if (args.tokens == 64 and args.path == 0 and achieved) else None,
                      "peak_source": pk["source"],
                      "kernel": "packed experts stage", "kernel_ms": head["experts_kernel_ms"],
                      "algorithmic_bytes": head["experts_bytes"], "active_experts": head["active_experts"]},
