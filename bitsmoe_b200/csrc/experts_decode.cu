@@ -32,6 +32,7 @@ namespace bm {
 
 constexpr int DEC_THREADS = 288;            // 8 compute warps + 1 producer warp
 constexpr int DEC_MAX_E = 1024;
+constexpr int DEC_CLASSES = 4;             // active experts are ordered by passes: >= 4, 3, 2, 1
 constexpr uint32_t DEC_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
   __shared__ DecStageInfo info[2];
   __shared__ __align__(8) uint64_t bar_full[2][2];   // [stage][everything but down | down words]
   __shared__ __align__(8) uint64_t bar_empty[2];
-  __shared__ int warp_cnt[9];
+  __shared__ int warp_cnt[DEC_CLASSES][9];
   const int slots_stride = dec_slots_stride(max_slots);
   const size_t unit_bytes_al = align_up_c(static_cast<size_t>(max_unit_bytes), 128);
   const size_t tabs_bytes_al = align_up_c(static_cast<size_t>(3) * (max_slots * 4 + 16), 128);
@@ -261,22 +262,55 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
     mbar_init(&bar_empty[1], 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // ---- compact the active experts (ascending id), 288 candidates per round
+  // ---- compact the active experts by descending number of passes (4 or more, 3, 2, 1 passes of FAST_MAX_TOK
+  // assignments), ascending id inside a class.  A CTA's first unit is taken from the END of the grid's first round
+  // (unit gridDim - 1 - blockIdx), its later ones from the front (blockIdx + k * gridDim), so the multi-pass units at
+  // the head of the list land on CTAs that do not get a unit of the last, partial round.
   int n_active = 0;
-  for (int base = 0; base < num_experts; base += DEC_THREADS) {
-    const int e = base + threadIdx.x;
-    const bool act = e < num_experts && expert_offsets[e + 1] > expert_offsets[e];
-    const unsigned m = __ballot_sync(0xffffffffu, act);
-    if (lane == 0) warp_cnt[warp] = __popc(m);
+  if (num_experts <= DEC_THREADS) {
+    const int e = threadIdx.x;
+    const int cnt = e < num_experts ? expert_offsets[e + 1] - expert_offsets[e] : 0;
+    const int passes = (cnt + FAST_MAX_TOK - 1) / FAST_MAX_TOK;
+    const int cls = cnt <= 0 ? -1 : (passes >= DEC_CLASSES ? 0 : DEC_CLASSES - passes);
+    unsigned mine = 0;
+#pragma unroll
+    for (int c = 0; c < DEC_CLASSES; ++c) {
+      const unsigned m = __ballot_sync(0xffffffffu, cls == c);
+      if (cls == c) mine = m;
+      if (lane == 0) warp_cnt[c][warp] = __popc(m);
+    }
     __syncthreads();
-    int before = n_active;
-    for (int w = 0; w < warp; ++w) before += warp_cnt[w];
-    if (act) active[before + __popc(m & ((1u << lane) - 1u))] = static_cast<int16_t>(e);
-    for (int w = 0; w < 9; ++w) n_active += warp_cnt[w];
+    int before = 0;
+#pragma unroll
+    for (int c = 0; c < DEC_CLASSES; ++c)
+      for (int w = 0; w < 9; ++w) {
+        const int n = warp_cnt[c][w];
+        n_active += n;
+        if (c < cls || (c == cls && w < warp)) before += n;
+      }
+    if (cls >= 0) active[before + __popc(mine & ((1u << lane) - 1u))] = static_cast<int16_t>(e);
     __syncthreads();
+  } else {
+    for (int c = 0; c < DEC_CLASSES; ++c) {
+      for (int base = 0; base < num_experts; base += DEC_THREADS) {
+        const int e = base + threadIdx.x;
+        const int cnt = e < num_experts ? expert_offsets[e + 1] - expert_offsets[e] : 0;
+        const int passes = (cnt + FAST_MAX_TOK - 1) / FAST_MAX_TOK;
+        const bool act = cnt > 0 && (passes >= DEC_CLASSES ? 0 : DEC_CLASSES - passes) == c;
+        const unsigned m = __ballot_sync(0xffffffffu, act);
+        if (lane == 0) warp_cnt[0][warp] = __popc(m);
+        __syncthreads();
+        int before = n_active;
+        for (int w = 0; w < warp; ++w) before += warp_cnt[0][w];
+        if (act) active[before + __popc(m & ((1u << lane) - 1u))] = static_cast<int16_t>(e);
+        for (int w = 0; w < 9; ++w) n_active += warp_cnt[0][w];
+        __syncthreads();
+      }
+    }
   }
   const int n_units = n_active * n_tiles;
-  if (static_cast<int>(blockIdx.x) >= n_units) return;
+  const int first_unit = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  if (first_unit >= n_units) return;
   bool ok = true;
   long long bm_tick_ = clock64();
   int* bm_timing_base = status + 8;
@@ -285,7 +319,7 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
   if (warp == 8) {
     // ------------------------------------------------------------------ producer warp
     int it = 0;
-    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++it) {
+    for (int u = first_unit; u < n_units; u = blockIdx.x + (it + 1) * gridDim.x, ++it) {
       const int buf = it & 1;
       const int e = active[u / n_tiles], tile = u % n_tiles;
       if (!mbar_wait(&bar_empty[buf], ((it >> 1) & 1) ^ 1)) { ok = false; break; }
@@ -337,7 +371,7 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(
 
   // -------------------------------------------------------------------- compute warps
   int it = 0;
-  for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++it) {
+  for (int u = first_unit; u < n_units && ok; u = blockIdx.x + (it + 1) * gridDim.x, ++it) {
     const int buf = it & 1;
     const uint32_t parity = (it >> 1) & 1;
     const int tile = u % n_tiles;
