@@ -210,7 +210,8 @@ __device__ __forceinline__ void decode_pass(const FastExpert& fe, const DecSmem&
 }
 
 // Persistent kernel.  Every CTA first compacts the list of experts that received tokens (from
-// expert_offsets), then walks the (active expert, tile) units u = blockIdx.x, blockIdx.x + gridDim.x, ...
+// expert_offsets, most passes first), then walks the (active expert, tile) units gridDim.x - 1 - blockIdx.x,
+// blockIdx.x + gridDim.x, blockIdx.x + 2 * gridDim.x, ...
 // Warp 8 is the producer: for each unit it waits until the target stage is released, fetches the expert
 // descriptor and the first pass's token ids / route weights, and starts bulk copies of the unit block, the
 // expert's slot tables and the tokens' h rows into one of two shared-memory stages; the 8 compute warps
