@@ -65,15 +65,16 @@ _SIGS = {
     "bm_layer_decode_codes": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "bm_layer_has_fast_layout": (C.c_int, [C.c_void_p]),
     "bm_layer_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "bm_layer_selftest_wait": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "bm_route_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p]),
     "bm_route_build_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "bm_route_max_tiles": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
-    "bm_route_build": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+    "bm_route_build": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                  C.c_void_p]),
     "bm_route_build_static_capacity": (C.c_size_t, []),
-    "bm_route_build_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+    "bm_route_build_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "bm_route": (C.c_int, [C.c_void_p, C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                            C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

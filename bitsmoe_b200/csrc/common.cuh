@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -40,6 +41,16 @@ int set_error(int status, const char* fmt, ...);
     if (_e != cudaSuccess)                                                                 \
       return ::bm::set_error(BM_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
   } while (0)
+
+// Set-up that belongs to a (kernel, device) pair -- cudaFuncSetAttribute, occupancy queries -- runs once per device
+// ordinal, not once per process: a second GPU driven from the same process needs its own.  Two host threads may both
+// run the set-up for a device (it is idempotent); the flag only publishes that it has been done.
+constexpr int MAX_DEVICES = 64;
+struct PerDeviceOnce {
+  std::atomic<unsigned char> done[MAX_DEVICES] = {};
+  bool is_done(int dev) const { return dev >= 0 && dev < MAX_DEVICES && done[dev].load(std::memory_order_acquire) != 0; }
+  void mark(int dev) { if (dev >= 0 && dev < MAX_DEVICES) done[dev].store(1, std::memory_order_release); }
+};
 
 // One packed matrix as the device sees it (pointers into the caller's buffers).
 struct MatDev {

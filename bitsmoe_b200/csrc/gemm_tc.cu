@@ -237,13 +237,15 @@ int launch_gemm_tc(const GemmTcArgs& a, int problems, cudaStream_t st) {
   BM_REQUIRE(a.K % TC_BK == 0, BM_ERR_UNSUPPORTED, "gemm_tc: K=%d must be a multiple of %d", a.K, TC_BK);
   BM_REQUIRE((reinterpret_cast<uintptr_t>(a.X) & 15u) == 0, BM_ERR_UNSUPPORTED, "gemm_tc: activations must be 16-byte aligned");
   BM_REQUIRE(a.N % 8 == 0, BM_ERR_UNSUPPORTED, "gemm_tc: N=%d must be a multiple of 8", a.N);
-  static bool attr_done = false;
+  static PerDeviceOnce attr_once;
+  int dev = -1;
+  BM_CUDA(cudaGetDevice(&dev));
   const int smem = TC_STAGES * TC_STAGE_BYTES;
-  if (!attr_done) {
+  if (!attr_once.is_done(dev)) {
     BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_done = true;
+    attr_once.mark(dev);
   }
   dim3 grid((a.M + TC_BM - 1) / TC_BM, (a.N + TC_BN - 1) / TC_BN, problems);
   if (a.x_dtype == BM_F32) gemm_tc_kernel<BM_F32><<<grid, TC_THREADS, smem, st>>>(a);

@@ -256,7 +256,7 @@ static LayerWs carve_layer_ws(const bm_layer* L, void* ws, int T, int k) {
 
 using namespace bm;
 
-extern "C" int bm_abi_version(void) { return 1; }
+extern "C" int bm_abi_version(void) { return 2; }
 extern "C" const char* bm_last_error(void) { return g_err; }
 extern "C" const char* bm_status_string(int s) {
   switch (s) {
@@ -409,7 +409,7 @@ static int basis_project_impl(const bm_layer_t* L, const void* x, int x_dtype, i
     }
     return launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
   }
-  if (L->hidden % 64 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && !getenv("BM_NO_TC")) {
+  if (L->hidden % 64 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
     GemmTcArgs t{};
     t.X = x; t.W[0] = L->vh_gate; t.W[1] = L->vh_up; t.C[0] = h_gate; t.C[1] = h_up; t.residual = nullptr;
     t.M = T; t.N = L->rank_in; t.K = L->hidden; t.x_dtype = x_dtype; t.c_dtype = BM_F16; t.status = L->status_dev;
@@ -457,7 +457,7 @@ static int experts_forward_impl(const bm_layer_t* L, const uint16_t* h_gate, con
              "experts_forward: null pointer");
   BM_REQUIRE(path != BM_PATH_TENSOR || L->fast_ok, BM_ERR_UNSUPPORTED,
              "experts_forward: the tensor path needs 1- to 4-bit rows and full tiles; this layer has neither");
-  if (L->fast_ok && (path == BM_PATH_TENSOR || (path == BM_PATH_AUTO && num_assign > 16 * L->num_experts && experts_tc_fits(L) && !getenv("BM_NO_TC"))))
+  if (L->fast_ok && (path == BM_PATH_TENSOR || (path == BM_PATH_AUTO && num_assign > 16 * L->num_experts && experts_tc_fits(L))))
     return launch_experts_tc(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up), token_indices,
                              expert_offsets, route_weights, T, rank_accum, st);
   BM_REQUIRE(path != BM_PATH_DECODE || L->fast_ok, BM_ERR_UNSUPPORTED,
@@ -496,7 +496,7 @@ extern "C" int bm_combine_down_basis(const bm_layer_t* L, const float* rank_accu
     a.splits = 1; a.mrows = 16;
     return launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
   }
-  if (L->rank_out % 64 == 0 && !getenv("BM_NO_TC")) {
+  if (L->rank_out % 64 == 0) {
     GemmTcArgs t{};
     t.X = rank_accum; t.W[0] = t.W[1] = L->u_down; t.C[0] = t.C[1] = y; t.residual = residual;
     t.M = T; t.N = L->hidden; t.K = L->rank_out; t.x_dtype = BM_F32; t.c_dtype = y_dtype; t.status = L->status_dev;

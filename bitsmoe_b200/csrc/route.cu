@@ -244,19 +244,26 @@ __device__ __forceinline__ void write_tile_table(const int* offsets /*[E+1] shar
   }
 }
 
+// Routed expert id of assignment i -> packed id, or -1 (dropped).  Ids outside [0, num_routed) -- a gate that is not
+// this library's own can hand in anything -- and map entries outside [0, E) are dropped instead of indexing with them.
+__device__ __forceinline__ int local_expert(const int32_t* __restrict__ topk_idx, const int32_t* __restrict__ g2l, int i,
+                                            int num_routed, int E) {
+  int e = topk_idx[i];
+  if (static_cast<unsigned>(e) >= static_cast<unsigned>(num_routed)) return -1;
+  if (g2l) e = g2l[e];
+  return static_cast<unsigned>(e) < static_cast<unsigned>(E) ? e : -1;
+}
+
 // A <= ROUTE_BLOCK: everything in one block.
 __global__ void __launch_bounds__(ROUTE_BLOCK) route_build_fused_kernel(
-    const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w, const int32_t* __restrict__ g2l, int A, int k,
-    int E, int tile_rows, int32_t* __restrict__ token_indices, int32_t* __restrict__ expert_offsets,
+    const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w, const int32_t* __restrict__ g2l, int num_routed,
+    int A, int k, int E, int tile_rows, int32_t* __restrict__ token_indices, int32_t* __restrict__ expert_offsets,
     float* __restrict__ route_flat, int32_t* __restrict__ tile_table, int max_tiles, int32_t* __restrict__ counts) {
   extern __shared__ __align__(16) unsigned char sm_raw[];
   RouteSmem s = carve_route_smem(sm_raw, E);
   const int i = threadIdx.x;
   int e = -1;
-  if (i < A) {
-    e = topk_idx[i];
-    if (g2l) e = g2l[e];
-  }
+  if (i < A) e = local_expert(topk_idx, g2l, i, num_routed, E);
   const int rank_w = block_count_and_rank(e, E, s);
   block_exclusive_scan(s.block_count, s.scan, E);
   for (int x = threadIdx.x; x <= E; x += blockDim.x) expert_offsets[x] = s.scan[x];
@@ -272,16 +279,13 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) route_build_fused_kernel(
 
 // A > ROUTE_BLOCK: count per block, scan across blocks, scatter.
 __global__ void __launch_bounds__(ROUTE_BLOCK) route_count_kernel(const int32_t* __restrict__ topk_idx,
-                                                                 const int32_t* __restrict__ g2l, int A, int E,
+                                                                 const int32_t* __restrict__ g2l, int num_routed, int A, int E,
                                                                  int32_t* __restrict__ block_hist /*[nblocks][E]*/) {
   extern __shared__ __align__(16) unsigned char sm_raw[];
   RouteSmem s = carve_route_smem(sm_raw, E);
   const int i = blockIdx.x * ROUTE_BLOCK + threadIdx.x;
   int e = -1;
-  if (i < A) {
-    e = topk_idx[i];
-    if (g2l) e = g2l[e];
-  }
+  if (i < A) e = local_expert(topk_idx, g2l, i, num_routed, E);
   block_count_and_rank(e, E, s);
   for (int x = threadIdx.x; x < E; x += blockDim.x) block_hist[static_cast<int64_t>(blockIdx.x) * E + x] = s.block_count[x];
 }
@@ -310,17 +314,14 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) route_scan_kernel(int32_t* __rest
 }
 
 __global__ void __launch_bounds__(ROUTE_BLOCK) route_scatter_kernel(
-    const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w, const int32_t* __restrict__ g2l, int A, int k,
-    int E, const int32_t* __restrict__ block_hist, const int32_t* __restrict__ expert_offsets,
+    const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w, const int32_t* __restrict__ g2l, int num_routed,
+    int A, int k, int E, const int32_t* __restrict__ block_hist, const int32_t* __restrict__ expert_offsets,
     int32_t* __restrict__ token_indices, float* __restrict__ route_flat) {
   extern __shared__ __align__(16) unsigned char sm_raw[];
   RouteSmem s = carve_route_smem(sm_raw, E);
   const int i = blockIdx.x * ROUTE_BLOCK + threadIdx.x;
   int e = -1;
-  if (i < A) {
-    e = topk_idx[i];
-    if (g2l) e = g2l[e];
-  }
+  if (i < A) e = local_expert(topk_idx, g2l, i, num_routed, E);
   const int rank_w = block_count_and_rank(e, E, s);
   if (e >= 0) {
     const int pos = expert_offsets[e] + block_hist[static_cast<int64_t>(blockIdx.x) * E + e] +
@@ -364,12 +365,15 @@ extern "C" size_t bm_route_build_workspace_bytes(int32_t T, int32_t k, int32_t n
   return bm::align_up(static_cast<size_t>(nblocks) * num_local * sizeof(int32_t), 256);
 }
 
-extern "C" int bm_route_build(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local, int32_t T,
+extern "C" int bm_route_build(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local,
+                              int32_t num_routed, int32_t T,
                               int32_t k, int32_t num_local, int32_t tile_rows, int32_t* token_indices,
                               int32_t* expert_offsets, float* route_flat, int32_t* tile_table, int32_t* counts,
                               void* workspace, size_t workspace_bytes, void* stream) {
   using namespace bm;
-  BM_REQUIRE(T >= 0 && k > 0 && num_local > 0, BM_ERR_INVALID_ARG, "route_build: bad sizes");
+  BM_REQUIRE(T >= 0 && k > 0 && num_local > 0 && num_routed > 0, BM_ERR_INVALID_ARG, "route_build: bad sizes");
+  BM_REQUIRE(global_to_local != nullptr || num_routed == num_local, BM_ERR_INVALID_ARG,
+             "route_build: %d routed experts but %d packed and no id map", num_routed, num_local);
   BM_REQUIRE(num_local <= ROUTE_MAX_E, BM_ERR_UNSUPPORTED, "route_build: %d experts exceed %d", num_local, ROUTE_MAX_E);
   BM_REQUIRE(tile_rows > 0, BM_ERR_INVALID_ARG, "route_build: tile_rows must be positive");
   BM_REQUIRE(expert_offsets, BM_ERR_INVALID_ARG, "route_build: null expert_offsets");
@@ -380,16 +384,18 @@ extern "C" int bm_route_build(const int32_t* topk_idx, const float* topk_w, cons
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int max_tiles = bm_route_max_tiles(T, k, num_local, tile_rows);
   const size_t smem = route_smem_bytes(num_local);
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDeviceOnce attr_once;
+  int dev = -1;
+  BM_CUDA(cudaGetDevice(&dev));
+  if (!attr_once.is_done(dev)) {
     const int big = static_cast<int>(route_smem_bytes(ROUTE_MAX_E));
     BM_CUDA(cudaFuncSetAttribute(route_build_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
     BM_CUDA(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
     BM_CUDA(cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    attr_done = true;
+    attr_once.mark(dev);
   }
   if (A <= ROUTE_BLOCK) {
-    route_build_fused_kernel<<<1, ROUTE_BLOCK, smem, st>>>(topk_idx, topk_w, global_to_local, A, k, num_local, tile_rows,
+    route_build_fused_kernel<<<1, ROUTE_BLOCK, smem, st>>>(topk_idx, topk_w, global_to_local, num_routed, A, k, num_local, tile_rows,
                                                            token_indices, expert_offsets, route_flat, tile_table,
                                                            max_tiles, counts);
     BM_LAUNCH_CHECK("route_build_fused_kernel");
@@ -400,12 +406,12 @@ extern "C" int bm_route_build(const int32_t* topk_idx, const float* topk_w, cons
   BM_REQUIRE(workspace && workspace_bytes >= need, BM_ERR_WORKSPACE, "route_build: workspace of %zu bytes needed, %zu given",
              need, workspace_bytes);
   int32_t* block_hist = static_cast<int32_t*>(workspace);
-  route_count_kernel<<<nblocks, ROUTE_BLOCK, smem, st>>>(topk_idx, global_to_local, A, num_local, block_hist);
+  route_count_kernel<<<nblocks, ROUTE_BLOCK, smem, st>>>(topk_idx, global_to_local, num_routed, A, num_local, block_hist);
   BM_LAUNCH_CHECK("route_count_kernel");
   route_scan_kernel<<<1, ROUTE_BLOCK, 0, st>>>(block_hist, nblocks, num_local, tile_rows, expert_offsets, tile_table,
                                                max_tiles, counts);
   BM_LAUNCH_CHECK("route_scan_kernel");
-  route_scatter_kernel<<<nblocks, ROUTE_BLOCK, smem, st>>>(topk_idx, topk_w, global_to_local, A, k, num_local, block_hist,
+  route_scatter_kernel<<<nblocks, ROUTE_BLOCK, smem, st>>>(topk_idx, topk_w, global_to_local, num_routed, A, k, num_local, block_hist,
                                                            expert_offsets, token_indices, route_flat);
   BM_LAUNCH_CHECK("route_scatter_kernel");
   return BM_OK;
@@ -419,6 +425,6 @@ extern "C" int bm_route(const void* logits, int logits_dtype, int32_t T, int32_t
   using namespace bm;
   int rc = bm_route_topk(logits, logits_dtype, T, E_routed, k, renorm, weight_round, topk_idx, topk_w, stream);
   if (rc) return rc;
-  return bm_route_build(topk_idx, topk_w, global_to_local, T, k, num_local, tile_rows, token_indices, expert_offsets,
-                        route_flat, tile_table, counts, workspace, workspace_bytes, stream);
+  return bm_route_build(topk_idx, topk_w, global_to_local, E_routed, T, k, num_local, tile_rows, token_indices,
+                        expert_offsets, route_flat, tile_table, counts, workspace, workspace_bytes, stream);
 }

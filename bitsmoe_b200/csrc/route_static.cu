@@ -15,8 +15,9 @@ namespace bm {
 constexpr size_t ROUTE_STATIC_SCRATCH_BYTES = 1u << 20;
 static __device__ __align__(256) unsigned char g_route_scratch[ROUTE_STATIC_SCRATCH_BYTES];
 
-constexpr int MAX_DEVICES = 64;
-static void* g_route_scratch_ptr[MAX_DEVICES] = {};   // device address of the array, per device
+// Device address of the array, per device ordinal.  Written without a lock: two host threads that race on the first
+// call for a device both look the address up and store the same value.
+static void* g_route_scratch_ptr[MAX_DEVICES] = {};
 
 // `g_route_scratch` in host code only names the symbol; the address a kernel can use has to be asked for,
 // once per device, with that device current.
@@ -38,8 +39,8 @@ static int route_scratch_address(void** out) {
 
 extern "C" size_t bm_route_build_static_capacity(void) { return bm::ROUTE_STATIC_SCRATCH_BYTES; }
 
-extern "C" int bm_route_build_static(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local, int32_t T,
-                                     int32_t k, int32_t num_local, int32_t tile_rows, int32_t* token_indices,
+extern "C" int bm_route_build_static(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local,
+                                     int32_t num_routed, int32_t T, int32_t k, int32_t num_local, int32_t tile_rows, int32_t* token_indices,
                                      int32_t* expert_offsets, float* route_flat, int32_t* tile_table, int32_t* counts,
                                      void* stream) {
   using namespace bm;
@@ -51,6 +52,6 @@ extern "C" int bm_route_build_static(const int32_t* topk_idx, const float* topk_
   void* scratch = nullptr;
   const int rc = route_scratch_address(&scratch);
   if (rc) return rc;
-  return bm_route_build(topk_idx, topk_w, global_to_local, T, k, num_local, tile_rows, token_indices, expert_offsets,
+  return bm_route_build(topk_idx, topk_w, global_to_local, num_routed, T, k, num_local, tile_rows, token_indices, expert_offsets,
                         route_flat, tile_table, counts, scratch, ROUTE_STATIC_SCRATCH_BYTES, stream);
 }

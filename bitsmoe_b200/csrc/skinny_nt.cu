@@ -235,10 +235,12 @@ int launch_skinny_nt(SkinnyArgs a, cudaStream_t st) {
   size_t smem = static_cast<size_t>(a.mrows + SK_NTOK) * (ks + 8) * 2;
   if (a.splits > 1) smem += static_cast<size_t>(a.mrows) * SK_NTOK * 4;
   BM_REQUIRE(smem <= 160 * 1024, BM_ERR_UNSUPPORTED, "skinny_nt: k-slice of %d does not fit shared memory", ks);
-  static bool attr_done = false;
-  if (!attr_done) {
+  static PerDeviceOnce attr_once;
+  int dev = -1;
+  BM_CUDA(cudaGetDevice(&dev));
+  if (!attr_once.is_done(dev)) {
     BM_CUDA(cudaFuncSetAttribute(skinny_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-    attr_done = true;
+    attr_once.mark(dev);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((a.rows_per_w * a.n_w / a.mrows) * a.splits);

@@ -28,10 +28,10 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Waits for the phase with the given parity, at most WAIT_LIMIT_NS of wall time: each probe suspends for
+// Waits for the phase with the given parity, at most limit_ns of wall time: each probe suspends for
 // up to ~20 us in hardware, and the elapsed time is checked between probes.  Returns false on timeout.
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t limit_ns = WAIT_LIMIT_NS) {
   const uint32_t addr = smem_u32(bar);
   uint64_t t0 = 0;
   for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
@@ -45,7 +45,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if ((i & 15u) == 15u) {
       const uint64_t now = global_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
   return false;

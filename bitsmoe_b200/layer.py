@@ -250,10 +250,12 @@ def route_build(topk_idx: torch.Tensor, topk_w: torch.Tensor, num_local: int,
     counts = torch.empty((2,), dtype=torch.int32, device=dev)
     need = int(lib.bm_route_build_workspace_bytes(T, k, num_local))
     ws = torch.empty(max(need, 1), dtype=torch.uint8, device=dev) if need else None
+    num_routed = num_local
     if global_to_local is not None:
         global_to_local = global_to_local.to(device=dev, dtype=torch.int32).contiguous()
+        num_routed = global_to_local.numel()
     with torch.cuda.device(dev):
-        capi.check(lib.bm_route_build(topk_idx.data_ptr(), topk_w.data_ptr(), capi.ptr(global_to_local), T, k, num_local,
+        capi.check(lib.bm_route_build(topk_idx.data_ptr(), topk_w.data_ptr(), capi.ptr(global_to_local), num_routed, T, k, num_local,
                                       tile_rows, tok.data_ptr(), off.data_ptr(), rw.data_ptr(), tiles.data_ptr(),
                                       counts.data_ptr(), capi.ptr(ws), need, capi.stream_ptr(dev)))
     return tok, off, rw, tiles, counts

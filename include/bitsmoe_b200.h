@@ -110,6 +110,12 @@ BM_API int bm_layer_has_fast_layout(const bm_layer_t* layer);
  * the last call (BM_ERR_TIMEOUT) -- the device-side counterpart of C10_CUDA_KERNEL_LAUNCH_CHECK. */
 BM_API int bm_layer_status(const bm_layer_t* layer, void* stream);
 
+/* No counterpart in the reference.  Launches a one-warp kernel whose only job is to wait (at most limit_us
+ * microseconds, 1..100000) on a barrier that nothing signals: the wait gives up, the kernel returns, and the next
+ * bm_layer_status() reports BM_ERR_TIMEOUT.  It is how the time-out path shared by all pipelines of this library
+ * is tested on a GPU without faulting or hanging it. */
+BM_API int bm_layer_selftest_wait(const bm_layer_t* layer, int32_t limit_us, void* stream);
+
 /* ---- routing -----------------------------------------------------------
  * Router tail of bitsmoe/models/qwen3moe/bitsmoe_block.py:47-51 (softmax in
  * fp32, top-k sorted by descending probability with ties to the lower expert
@@ -126,9 +132,11 @@ BM_API size_t bm_route_build_workspace_bytes(int32_t T, int32_t k, int32_t num_l
  *   tile_table int32 [max_tiles, 3] = (expert, first assignment, rows <= tile_rows), padded
  *              with rows == 0 entries up to max_tiles = bm_route_max_tiles(); may be NULL
  *   counts int32 [2] = {assignments kept, tiles}; may be NULL
- * global_to_local int32 [E] maps a routed expert id to a packed id or -1 (NULL = identity). */
+ * global_to_local int32 [num_routed] maps a routed expert id to a packed id or -1 (NULL = identity, and then
+ * num_routed must equal num_local).  Ids come from the caller's gate: an id outside [0, num_routed), or a map
+ * entry outside [0, num_local), is treated as -1 -- the assignment is dropped, nothing is indexed with it. */
 BM_API int32_t bm_route_max_tiles(int32_t T, int32_t k, int32_t num_local, int32_t tile_rows);
-BM_API int bm_route_build(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local,
+BM_API int bm_route_build(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local, int32_t num_routed,
                    int32_t T, int32_t k, int32_t num_local, int32_t tile_rows,
                    int32_t* token_indices, int32_t* expert_offsets, float* route_flat,
                    int32_t* tile_table, int32_t* counts, void* workspace, size_t workspace_bytes, void* stream);
@@ -146,7 +154,7 @@ BM_API int bm_route_build(const int32_t* topk_idx, const float* topk_w, const in
  *    calls whose kernels overlap on the GPU (different streams) race on it. */
 BM_API size_t bm_route_build_static_capacity(void);
 BM_API int bm_route_build_static(const int32_t* topk_idx, const float* topk_w, const int32_t* global_to_local,
-                                 int32_t T, int32_t k, int32_t num_local, int32_t tile_rows,
+                                 int32_t num_routed, int32_t T, int32_t k, int32_t num_local, int32_t tile_rows,
                                  int32_t* token_indices, int32_t* expert_offsets, float* route_flat,
                                  int32_t* tile_table, int32_t* counts, void* stream);
 

@@ -111,7 +111,7 @@ def build(reference: str, force: bool = False) -> None:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a BitsMoE source tree")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     if not os.path.isdir(a.reference):

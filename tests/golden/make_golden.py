@@ -70,7 +70,7 @@ def u32(t: torch.Tensor) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a BitsMoE source tree")
     a = ap.parse_args()
     rquant, rpacker = import_reference(a.reference)
     g = torch.Generator().manual_seed(42)

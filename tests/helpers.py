@@ -88,13 +88,40 @@ def ref_args(layer: synth.SynthLayer, device) -> list:
     return out
 
 
-def assert_close(got: torch.Tensor, want: torch.Tensor, rtol: float = RTOL, atol: float = ATOL, what: str = "") -> None:
-    got, want = got.detach().float().cpu(), want.detach().float().cpu()
+def assert_close(got: torch.Tensor, want: torch.Tensor, rtol: float = RTOL, atol: float = ATOL, what: str = "",
+                 rel_max: float = 2e-2, rel_l2: float = 1e-2) -> None:
+    """Element-wise ``|err| <= atol + rtol*|want|`` AND two bounds relative to the size of the expected signal:
+    ``max|err| <= rel_max * max|want|`` and ``||err||_2 <= rel_l2 * ||want||_2``.  The synthetic layers produce
+    outputs of order 1e-3 .. 1e-2, far below the absolute tolerance of the specification, so the element-wise test
+    alone would accept an all-zero result; the relative bounds are what makes a wrong kernel fail."""
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} != {tuple(want.shape)}"
+    assert bool(torch.isfinite(got).all()), f"{what}: non-finite values"
     err = (got - want).abs()
     bound = atol + rtol * want.abs()
     bad = err > bound
     assert not bool(bad.any()), (f"{what}: {int(bad.sum())}/{bad.numel()} outside rtol={rtol} atol={atol}; "
                                  f"max abs err {float(err.max()):.4g}, max |want| {float(want.abs().max()):.4g}")
+    if want.numel() == 0:
+        return
+    peak = float(want.abs().max())
+    if peak == 0.0:
+        assert float(err.max()) == 0.0, f"{what}: expected exact zeros, max |got| {float(got.abs().max()):.4g}"
+        return
+    assert float(err.max()) <= rel_max * peak, (f"{what}: max abs err {float(err.max()):.4g} > {rel_max} * max|want| "
+                                                f"({peak:.4g})")
+    l2 = float(torch.linalg.vector_norm(got - want)) / float(torch.linalg.vector_norm(want))
+    assert l2 <= rel_l2, f"{what}: relative L2 error {l2:.4g} > {rel_l2}"
+
+
+def assert_detects_damage(got: torch.Tensor, want: torch.Tensor, what: str = "", **tol) -> None:
+    """The check used on ``got`` must reject a halved result and a result with one row's signal removed: proof
+    that the tolerance can see a wrong kernel at this shape and scale."""
+    import pytest
+    with pytest.raises(AssertionError):
+        assert_close(got * 0.5, want, what=what + " (halved)", **tol)
+    with pytest.raises(AssertionError):
+        assert_close(torch.zeros_like(got), want, what=what + " (zeroed)", **tol)
 
 
 class LazyDecodedExperts:

@@ -53,6 +53,27 @@ def test_bitplane_errors():
     assert out.shape == (0, 2)
 
 
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 6, 8])
+def test_quantize_symmetric_on_device_matches_golden(bits):
+    """The quantiser that builds every synthetic layer runs on the GPU: its codes must be the ones the reference's
+    quantize_symmetric produced for the golden inputs (and the CPU oracle reproduces), its scales equal to rounding."""
+    import os
+    from bitsmoe_b200.quant import packer as ppacker
+    from bitsmoe_b200.quant.quantizer import quantize_symmetric
+    G = np.load(os.path.join(os.path.dirname(__file__), "golden", "format_golden.npz"))
+    for tag, dim in (("full", 2), ("tail", 1)):
+        x = torch.from_numpy(G[f"quant_x_{tag}"])
+        q, s = quantize_symmetric(x.to(DEV), bits=bits, dim=dim)
+        assert np.array_equal(q.cpu().numpy(), G[f"quant_q_{tag}_b{bits}"]), (tag, bits)
+        assert np.allclose(s.cpu().numpy(), G[f"quant_s_{tag}_b{bits}"], rtol=2e-6, atol=0), (tag, bits)
+    # the row-batched form used by synth.make_layer (full tiles and a ragged last tile), device against host
+    rows = torch.randn(96, 3 * 128 + 40, generator=torch.Generator().manual_seed(bits)) * 0.02
+    q_dev, s_dev = ppacker.quantize_rows(rows.to(DEV), bits)
+    q_cpu, s_cpu = ppacker.quantize_rows(rows, bits)
+    assert torch.equal(q_dev.cpu(), q_cpu)
+    assert torch.allclose(s_dev.cpu(), s_cpu, rtol=2e-6, atol=0)
+
+
 @pytest.fixture(scope="module")
 def mixed():
     layer = helpers.mixed_everything_layer()
@@ -290,12 +311,35 @@ def test_tensor_core_basis_products_vs_oracle(q30_small, T):
     packed.check_status()
     helpers.assert_close(hg, oforward.basis_project(x, layer.vh_gate.cpu()), rtol=2e-3, atol=2e-3, what="h_gate (tcgen05)")
     helpers.assert_close(hu, oforward.basis_project(x, layer.vh_up.cpu()), rtol=2e-3, atol=2e-3, what="h_up (tcgen05)")
+    _check_down_basis(packed, layer, T)
+
+
+def _check_down_basis(packed, layer, T):
+    """y = fp16(acc) . U_down^T alone at 2e-3 of its peak, then with a residual of the same scale, in every output
+    type: an error in the product cannot hide under the residual."""
+    cfg = layer.cfg
     acc = torch.randn(T, cfg.rank) * 0.05
-    res = torch.randn(T, cfg.hidden).to(torch.bfloat16)
-    y = packed.combine_down_basis(acc.to(DEV), torch.bfloat16, residual=res.to(DEV))
-    packed.check_status()
-    want = oforward.down_basis(acc, layer.u_down.cpu(), torch.float32) + res.float()
-    helpers.assert_close(y, want, rtol=1e-2, atol=1e-2, what="down basis + residual (tcgen05)")
+    prod = oforward.down_basis(acc, layer.u_down.cpu(), torch.float32)
+    peak = float(prod.abs().max())
+    res = torch.randn(T, cfg.hidden) * float(prod.std())
+    for dt, eps in ((torch.float32, 2e-3), (torch.float16, 2e-3), (torch.bfloat16, 6e-3)):
+        y = packed.combine_down_basis(acc.to(DEV), dt)
+        packed.check_status()
+        assert y.dtype == dt
+        helpers.assert_close(y, prod, rtol=0.0, atol=eps * peak, rel_max=eps, what=f"down basis product, {dt}")
+        helpers.assert_detects_damage(y, prod, rtol=0.0, atol=eps * peak, rel_max=eps)
+        r = res.to(dt)
+        y2 = packed.combine_down_basis(acc.to(DEV), dt, residual=r.to(DEV))
+        helpers.assert_close(y2, prod + r.float(), rtol=0.0, atol=2 * eps * peak, rel_max=2 * eps, what=f"down basis + residual, {dt}")
+        # the add itself: the difference of the two outputs is the residual, up to one rounding of each output
+        helpers.assert_close(y2.float() - y.float(), r.float(), rtol=0.0, atol=3 * eps * peak, rel_max=1.0, rel_l2=1.0,
+                             what=f"residual add, {dt}")
+
+
+@pytest.mark.parametrize("T", [1, 7, 64, 256])
+def test_skinny_down_basis_product(q30_small, T):
+    layer, packed, _ = q30_small
+    _check_down_basis(packed, layer, T)
 
 
 @pytest.mark.parametrize("T", [5, 64, 200, 1000])
@@ -385,3 +429,40 @@ def test_fast_paths_shape_sweep(case):
             helpers.assert_close(got, gen, rtol=1e-2, atol=3e-4, what=f"sweep {case} T={T} path={path} vs generic")
         y = packed.forward(x.to(DEV), logits.to(DEV), cfg.top_k, True, torch.bfloat16)
         helpers.assert_close(y, o["y_fp32"], what=f"sweep {case} T={T} layer output")
+
+
+def test_route_build_drops_out_of_range_ids():
+    """Expert ids come from the caller's gate (DeepSeek's is third-party code): an id outside the routed range, or a map
+    entry outside the packed range, drops the assignment and never indexes anything."""
+    E = 6
+    idx = torch.tensor([[0, 5], [99, 2], [-3, 1], [2, 1 << 30]], dtype=torch.int32)
+    w = torch.arange(1, 9, dtype=torch.float32).reshape(4, 2)
+    tok, off, rw, _, counts = route_build(idx.to(DEV), w.to(DEV), E)
+    assert off.cpu().tolist() == [0, 1, 2, 4, 4, 4, 5]
+    assert counts.cpu().tolist()[0] == 5
+    assert tok.cpu()[:5].tolist() == [0, 2, 1, 3, 0]
+    assert rw.cpu()[:5].tolist() == [1.0, 6.0, 4.0, 7.0, 2.0]
+    # with a map: entries that point outside the packed experts drop too
+    g2l = torch.tensor([0, 7, 1, -1, -5, 2], dtype=torch.int32)
+    tok, off, rw, _, counts = route_build(idx.to(DEV), w.to(DEV), 3, g2l.to(DEV))
+    assert off.cpu().tolist() == [0, 1, 3, 4]
+    assert tok.cpu()[:4].tolist() == [0, 1, 3, 0]
+    # large batch: the multi-block kernels take the same care
+    big = torch.randint(-4, E + 4, (3000, 2), dtype=torch.int32)
+    tok, off, rw, _, counts = route_build(big.to(DEV), torch.ones(3000, 2).to(DEV), E)
+    keep = (big >= 0) & (big < E)
+    assert int(counts.cpu()[0]) == int(keep.sum())
+    assert off.cpu().tolist()[1:] == torch.cumsum(torch.bincount(big[keep].long(), minlength=E), 0).tolist()
+
+
+def test_bounded_wait_gives_up_and_reports_timeout(q30_small):
+    """The pipelines' waits are bounded: a wait that nothing satisfies returns after its limit, the kernel exits
+    normally, the status flag reports BM_ERR_TIMEOUT once, and the context keeps working."""
+    _, packed, _ = q30_small
+    lib = capi.lib()
+    with torch.cuda.device(DEV):
+        assert lib.bm_layer_selftest_wait(packed._handle, 1000, capi.stream_ptr(torch.device(DEV))) == capi.BM_OK
+        with pytest.raises(capi.BitsMoEError, match="bounded wait"):
+            packed.check_status()
+        packed.check_status()                      # the flag was cleared by the report
+    assert float(torch.ones(4, device=DEV).sum()) == 4.0

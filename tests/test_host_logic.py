@@ -103,7 +103,7 @@ def test_c_abi_exports_every_declared_symbol():
     handle = ctypes.CDLL(capi.LIB_PATH)
     for name in declared:
         assert hasattr(handle, name), name
-    assert capi.lib().bm_abi_version() == 1
+    assert capi.lib().bm_abi_version() == 2
     assert capi.lib().bm_status_string(5) == b"device wait timed out"
 
 

@@ -26,7 +26,7 @@ def _static_build(idx, w, num_local, tile_rows=128):
     tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=DEV)
     counts = torch.empty((2,), dtype=torch.int32, device=DEV)
     with torch.cuda.device(DEV):
-        status = lib.bm_route_build_static(idx.data_ptr(), w.data_ptr(), None, T, k, num_local, tile_rows, tok.data_ptr(),
+        status = lib.bm_route_build_static(idx.data_ptr(), w.data_ptr(), None, num_local, T, k, num_local, tile_rows, tok.data_ptr(),
                                            off.data_ptr(), rw.data_ptr(), tiles.data_ptr(), counts.data_ptr(),
                                            capi.stream_ptr(torch.device(DEV)))
     return status, (tok, off, rw, tiles, counts)
