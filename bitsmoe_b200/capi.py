@@ -65,6 +65,7 @@ _SIGS = {
     "bm_layer_decode_codes": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "bm_layer_has_fast_layout": (C.c_int, [C.c_void_p]),
     "bm_layer_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "bm_layer_set_option": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
     "bm_layer_selftest_wait": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "bm_route_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -96,7 +96,7 @@ struct FastExpert {
   FastMat m[3];
   int64_t unit_base;    // byte offset of tile 0's unit block from arena base
   int32_t unit_bytes;   // bytes per unit block (multiple of 128)
-  int32_t sec_off[6];   // byte offsets inside a unit: scale g,u,d then words g,u,d
+  int32_t sec_off[6];   // byte offsets inside a unit: [0..2] scales of g,u,d, [3..5] words of g,u,d; sec_off[3+m] == sec_off[m] + 2 * nslots(m)
   int32_t pad_;
 };
 
@@ -165,6 +165,10 @@ struct bm_layer {
   const bm::FastExpert* fast_dev = nullptr;   // in the arena
   std::vector<bm::FastExpert> fast_host;
   int max_unit_bytes = 0, max_slots = 0, max_words = 0;
+  // launch geometry of the decode kernel on this layer's device (plan_experts_decode)
+  bool dec_ok = false;
+  int dec_ring = 0, dec_sec_bytes = 0, dec_grid = 0, dec_act_bufs = 2, dec_ctas = 0, dec_force_ctas = 0;
+  size_t dec_smem = 0;
   int* status_dev = nullptr;       // device flag set by a kernel whose bounded wait gave up
   cudaStream_t side_stream = nullptr;   // routing runs here, beside the basis projection
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;

@@ -6,7 +6,7 @@
 // operations per code.  At layer creation every expert is repacked into one contiguous block per
 // (expert, 128-column tile):
 //
-//   unit block = [scale_gate | scale_up | scale_down | words_gate | words_up | words_down]
+//   unit block = [scale_gate | words_gate | scale_up | words_up | scale_down | words_down]
 //
 // in which a 32-bit word is the property of ONE thread of an m16n8k16 MMA (lane = 4 g + t) and
 // expands into A-fragment registers with one mask (and at most one shift) per register:

@@ -51,8 +51,10 @@ void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P);
 int build_fast(bm_layer* L, const FastPlan& P, cudaStream_t st);
 size_t fast_build_scratch_bytes(const FastPlan& P);
 int launch_arena_decode(const bm_layer* L, int e, int w, int8_t* codes, cudaStream_t st);
+int plan_experts_decode(bm_layer* L);
 int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
-                          const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
+                          const int32_t* expert_offsets, const float* route_w, int T, int num_assign, float* rank_accum,
+                          cudaStream_t st);
 bool experts_tc_fits(const bm_layer* L);
 int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                       const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
@@ -323,6 +325,8 @@ extern "C" int bm_layer_create(const bm_layer_desc_t* desc, void* arena, size_t 
     rc = build_fast(L, P, st);
     if (rc) { delete L; return rc; }
     L->fast_ok = true;
+    rc = plan_experts_decode(L);
+    if (rc) { delete L; return rc; }
   }
   // host-side objects for the fork/join of routing and basis projection (no device memory)
   if (cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
@@ -348,6 +352,20 @@ extern "C" int bm_layer_destroy(bm_layer_t* layer) {
 extern "C" int64_t bm_layer_expert_bytes(const bm_layer_t* L, int32_t e) {
   if (!L || e < 0 || e >= L->num_experts) return -1;
   return L->host[0][e].bytes + L->host[1][e].bytes + L->host[2][e].bytes;
+}
+
+extern "C" int bm_layer_set_option(bm_layer_t* L, int32_t option, int32_t value) {
+  BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "set_option: null layer");
+  BM_REQUIRE(option == BM_OPT_DECODE_CTAS_PER_SM, BM_ERR_INVALID_ARG, "set_option: unknown option %d", option);
+  BM_REQUIRE(value >= 0 && value <= 3, BM_ERR_INVALID_ARG, "set_option: CTAs per SM must be 0..3");
+  const bm_layer saved = *L;
+  L->dec_force_ctas = value;
+  const int rc = plan_experts_decode(L);
+  if (rc || (saved.dec_ok && !L->dec_ok)) {
+    *L = saved;
+    return rc ? rc : set_error(BM_ERR_UNSUPPORTED, "set_option: %d CTAs per SM do not fit this layer", value);
+  }
+  return BM_OK;
 }
 
 extern "C" int bm_layer_has_fast_layout(const bm_layer_t* L) { return L && L->fast_ok ? 1 : 0; }
@@ -462,9 +480,9 @@ static int experts_forward_impl(const bm_layer_t* L, const uint16_t* h_gate, con
                              expert_offsets, route_weights, T, rank_accum, st);
   BM_REQUIRE(path != BM_PATH_DECODE || L->fast_ok, BM_ERR_UNSUPPORTED,
              "experts_forward: the decode path needs 1- to 4-bit rows and full tiles; this layer has neither");
-  if (L->fast_ok && path != BM_PATH_GENERIC)
+  if (L->fast_ok && (path == BM_PATH_DECODE || (path != BM_PATH_GENERIC && L->dec_ok && num_assign / 8 + L->num_experts < 60000)))
     return launch_experts_decode(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
-                                 token_indices, expert_offsets, route_weights, T, rank_accum, st);
+                                 token_indices, expert_offsets, route_weights, T, num_assign, rank_accum, st);
   return launch_experts_generic(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
                                 token_indices, expert_offsets, route_weights, T, rank_accum, st);
 }

@@ -110,6 +110,12 @@ BM_API int bm_layer_has_fast_layout(const bm_layer_t* layer);
  * the last call (BM_ERR_TIMEOUT) -- the device-side counterpart of C10_CUDA_KERNEL_LAUNCH_CHECK. */
 BM_API int bm_layer_status(const bm_layer_t* layer, void* stream);
 
+/* No counterpart in the reference.  Tuning knobs of a layer; set between forwards, never while one is in flight.
+ *   BM_OPT_DECODE_CTAS_PER_SM: resident CTAs per SM of the decode kernel (1, 2 or 3; 0 = the library's choice).
+ * Returns BM_ERR_UNSUPPORTED when the layer's working set does not fit the requested geometry (nothing changes). */
+enum { BM_OPT_DECODE_CTAS_PER_SM = 0 };
+BM_API int bm_layer_set_option(bm_layer_t* layer, int32_t option, int32_t value);
+
 /* No counterpart in the reference.  Launches a one-warp kernel whose only job is to wait (at most limit_us
  * microseconds, 1..100000) on a barrier that nothing signals: the wait gives up, the kernel returns, and the next
  * bm_layer_status() reports BM_ERR_TIMEOUT.  It is how the time-out path shared by all pipelines of this library
