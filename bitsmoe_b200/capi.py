@@ -67,6 +67,11 @@ _SIGS = {
     "bm_layer_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "bm_layer_set_option": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
     "bm_layer_selftest_wait": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "bm_ep_flag_bytes": (C.c_size_t, []),
+    "bm_ep_barrier": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "bm_ep_push": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "bm_ep_pull_reduce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                    C.c_void_p, C.c_void_p]),
     "bm_route_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p]),
     "bm_route_build_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),

@@ -263,3 +263,165 @@ class GatherExpertParallel:
             full[: part.shape[0]] = part
             mine = full.view(G, 2, T, rank_out)[:, 0].contiguous()
         return _reduce_scatter_rows(mine, self.group)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Prefill-sized batches on one NVLink box: exchange through peer memory, no collective library on the data
+# path, no data-dependent sizes, no host synchronisation.
+#
+# Every rank maps one receive area of every other rank (torch's symmetric memory: one allocation per rank,
+# exchanged once at construction).  A wave of T tokens per rank then runs, stream-ordered on every rank:
+#
+#   top-k and basis projection write into the rank's own slice of its area
+#   bm_ep_push        rows to the ranks that own one of the token's experts (once per (token, destination)),
+#                     top-k of every token to every rank
+#   barrier
+#   routing build over all G*T tokens with a map that keeps this rank's experts, packed experts straight
+#   out of the receive area into the partial rank_accum of the wave
+#   barrier
+#   bm_ep_pull_reduce the token's home rank adds the partial rows of the ranks that contributed, ascending
+#   down basis (+ residual)
+#
+# Two waves alternate between two areas (and two streams) so that one wave's exchange can run beside the
+# other's expert kernel.
+# ---------------------------------------------------------------------------------------------------------
+class SymmetricExpertParallel:
+    """Expert-parallel forward of one packed layer over the ranks of ``group`` (all on one NVLink domain).
+
+    ``packed`` is this rank's ``PackedLayer`` (its slice of the experts plus the replicated basis),
+    ``wave_tokens`` the number of tokens per rank and wave (the same on every rank)."""
+
+    AREAS = 2
+
+    def __init__(self, packed, num_experts: int, top_k: int, wave_tokens: int, norm_topk_prob: bool = True,
+                 group=None):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm
+        from . import capi
+        self._C, self._capi = C, capi
+        self.packed, self.group = packed, group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if num_experts % self.world:
+            raise ValueError(f"{num_experts} experts do not shard over {self.world} ranks")
+        self.per = num_experts // self.world
+        if packed.num_experts != self.per:
+            raise ValueError(f"this rank's layer holds {packed.num_experts} experts, expected {self.per}")
+        self.top_k, self.norm_topk_prob, self.T = top_k, norm_topk_prob, int(wave_tokens)
+        dev = packed.device
+        G, T, k, r, r_out = self.world, self.T, top_k, packed.rank_in, packed.rank_out
+        align = lambda n: (n + 255) // 256 * 256
+        self.h_bytes = align(2 * G * T * r * 2)
+        self.r_bytes = align(2 * G * T * k * 4)
+        self.p_bytes = align(G * T * r_out * 4)
+        self.area_bytes = self.h_bytes + self.r_bytes + self.p_bytes
+        flag_bytes = align(int(capi.lib().bm_ep_flag_bytes()))
+        self.buf = symm.empty(self.AREAS * self.area_bytes + flag_bytes, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        self.hdl = symm.rendezvous(self.buf, self.group)
+        ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        Arr = C.c_void_p * G
+        self._tabs = []
+        for a in range(self.AREAS):
+            base = [p + a * self.area_bytes for p in ptrs]
+            self._tabs.append((Arr(*base), Arr(*[b + self.h_bytes for b in base]),
+                               Arr(*[b + self.h_bytes + self.r_bytes for b in base])))
+        self._flags = Arr(*[p + self.AREAS * self.area_bytes for p in ptrs])
+        self.barrier_limit_ms = 5000
+        g2l = torch.full((num_experts,), -1, dtype=torch.int32)
+        g2l[self.rank * self.per:(self.rank + 1) * self.per] = torch.arange(self.per, dtype=torch.int32)
+        self.g2l = g2l.to(dev)
+        # per-area scratch of the routing build over the G*T tokens of a wave, and of the combine
+        lib = capi.lib()
+        A = G * T * k
+        self._ws_bytes = int(lib.bm_route_build_workspace_bytes(G * T, k, self.per))
+        self._scratch = []
+        for _ in range(self.AREAS):
+            self._scratch.append(dict(
+                tok=torch.empty(A, dtype=torch.int32, device=dev), off=torch.empty(self.per + 1, dtype=torch.int32, device=dev),
+                rw=torch.empty(A, dtype=torch.float32, device=dev),
+                ws=torch.empty(max(self._ws_bytes, 256), dtype=torch.uint8, device=dev),
+                acc=torch.empty((T, r_out), dtype=torch.float32, device=dev)))
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(self.AREAS)]
+        torch.cuda.synchronize(dev)          # the zeroed flag area is in place before any peer signals into it
+        dist.barrier(group=self.group)
+
+    # views into this rank's own area ------------------------------------------------------------------
+    def _own(self, area: int):
+        G, T, k, r = self.world, self.T, self.top_k, self.packed.rank_in
+        base = area * self.area_bytes
+        h = self.buf[base: base + 2 * G * T * r * 2].view(torch.float16).view(2, G, T, r)
+        rt = self.buf[base + self.h_bytes: base + self.h_bytes + 2 * G * T * k * 4].view(torch.int32).view(2, G, T, k)
+        part = self.buf[base + self.h_bytes + self.r_bytes: base + self.h_bytes + self.r_bytes + G * T * self.packed.rank_out * 4]
+        return h, rt, part.view(torch.float32).view(G * T, self.packed.rank_out)
+
+    def nvlink_bytes_per_wave(self, topk_idx: torch.Tensor) -> Tuple[int, int]:
+        """(bytes this rank pushes, bytes it pulls) for the given routing of its tokens -- bookkeeping for reports."""
+        dest = expert_owner(topk_idx.long(), self.per)
+        pair = torch.zeros((topk_idx.shape[0], self.world), dtype=torch.bool, device=topk_idx.device)
+        pair.scatter_(1, dest, True)
+        pair[:, self.rank] = False
+        rows = int(pair.sum())
+        push = rows * 2 * self.packed.rank_in * 2 + topk_idx.shape[0] * self.top_k * 8 * (self.world - 1)
+        return push, rows * self.packed.rank_out * 4
+
+    def forward_wave(self, x: torch.Tensor, logits: torch.Tensor, weight_dtype, out: torch.Tensor,
+                     residual: Optional[torch.Tensor] = None, area: int = 0) -> torch.Tensor:
+        """One wave on the current stream: x [T, H], logits [T, E] of this rank's tokens -> out [T, H]."""
+        capi, lib, pk = self._capi, self._capi.lib(), self.packed
+        G, T, k, r, r_out = self.world, self.T, self.top_k, pk.rank_in, pk.rank_out
+        if x.shape[0] != T:
+            raise ValueError(f"a wave holds {T} tokens per rank, got {x.shape[0]}")
+        h, rt, part = self._own(area)
+        sc = self._scratch[area]
+        h_tab, r_tab, p_tab = self._tabs[area]
+        st = capi.stream_ptr(pk.device)
+        x, logits = x.contiguous(), logits.contiguous()
+        with torch.cuda.device(pk.device):
+            idx_mine, w_mine = rt[0, self.rank], rt[1, self.rank]
+            capi.check(lib.bm_route_topk(logits.data_ptr(), capi.dtype_code(logits.dtype), T, logits.shape[1], k,
+                                         int(bool(self.norm_topk_prob)), capi.round_code(weight_dtype), idx_mine.data_ptr(),
+                                         w_mine.data_ptr(), st))
+            capi.check(lib.bm_basis_project(pk._handle, x.data_ptr(), capi.dtype_code(x.dtype), T, h[0, self.rank].data_ptr(),
+                                            h[1, self.rank].data_ptr(), st))
+            capi.check(lib.bm_ep_push(h_tab, r_tab, G, self.rank, T, r, k, self.per, st))
+            capi.check(lib.bm_ep_barrier(pk._handle, self._flags, G, self.rank, 2 * area, self.barrier_limit_ms, st))
+            capi.check(lib.bm_route_build(rt[0].data_ptr(), rt[1].data_ptr(), self.g2l.data_ptr(), self.g2l.numel(), G * T, k,
+                                          self.per, 128, sc["tok"].data_ptr(), sc["off"].data_ptr(), sc["rw"].data_ptr(), None,
+                                          None, sc["ws"].data_ptr(), sc["ws"].numel(), st))
+            capi.check(lib.bm_experts_forward(pk._handle, h[0].data_ptr(), h[1].data_ptr(), sc["tok"].data_ptr(),
+                                              sc["off"].data_ptr(), sc["rw"].data_ptr(), G * T, G * T * k, part.data_ptr(),
+                                              capi.PATH_AUTO, None, 0, st))
+            capi.check(lib.bm_ep_barrier(pk._handle, self._flags, G, self.rank, 2 * area + 1, self.barrier_limit_ms, st))
+            capi.check(lib.bm_ep_pull_reduce(p_tab, idx_mine.data_ptr(), G, self.rank, T, r_out, k, self.per,
+                                             sc["acc"].data_ptr(), st))
+            if residual is not None:
+                residual = residual.to(x.dtype).contiguous()
+            capi.check(lib.bm_combine_down_basis(pk._handle, sc["acc"].data_ptr(), T, capi.ptr(residual), out.data_ptr(),
+                                                 capi.dtype_code(out.dtype), st))
+        return out
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, weight_dtype=torch.float16,
+                residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                overlap: bool = True) -> torch.Tensor:
+        """x [n*T, H] -> y [n*T, H] in n waves of T tokens; with ``overlap`` consecutive waves alternate between two
+        streams (and two receive areas), so one wave's exchange runs beside the other's expert kernel."""
+        T = self.T
+        if x.shape[0] % T:
+            raise ValueError(f"{x.shape[0]} tokens are not a whole number of waves of {T}")
+        n = x.shape[0] // T
+        y = out if out is not None else torch.empty_like(x)
+        cur = torch.cuda.current_stream(self.packed.device)
+        if not overlap or n == 1:
+            for w in range(n):
+                s = slice(w * T, (w + 1) * T)
+                self.forward_wave(x[s], logits[s], weight_dtype, y[s], None if residual is None else residual[s], area=w % self.AREAS)
+            return y
+        for st in self.streams:
+            st.wait_stream(cur)
+        for w in range(n):
+            s = slice(w * T, (w + 1) * T)
+            with torch.cuda.stream(self.streams[w % self.AREAS]):
+                self.forward_wave(x[s], logits[s], weight_dtype, y[s], None if residual is None else residual[s], area=w % self.AREAS)
+        for st in self.streams:
+            cur.wait_stream(st)
+        return y

@@ -199,6 +199,33 @@ BM_API int bm_layer_forward(const bm_layer_t* layer, const void* x, int x_dtype,
                      const int32_t* global_to_local, const void* residual, void* y, int32_t path,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- expert parallelism ------------------------------------------------
+ * The reference has no distributed code (bitsmoe/models/deepseekv2/bitsmoe_block.py:57-62 copies ep_size / ep_rank and
+ * never reads them).  These two kernels are the exchange that sharding the experts over the GPUs of one box needs; they
+ * move rank-space rows through memory that every rank has mapped (peer pointers over NVLink), with plain stores and
+ * loads.  One wave = T tokens on every one of `world` ranks; rank g owns experts [g * experts_per_rank, (g+1) * ...).
+ * Receive area of a rank (all pointer tables are HOST arrays of `world` DEVICE pointers, entry g = rank g's area):
+ *   h_bufs      fp16  [2][world][T][r]     gate rows of every rank's tokens, then up rows (token u = s*T + t)
+ *   route_bufs  int32 [2][world][T][k]     expert ids, then the bit patterns of the fp32 route weights
+ *   part_bufs   fp32  [world*T][r_out]     that rank's partial rank_accum (output of bm_experts_forward over all tokens)
+ * The caller separates the stages with barriers across the ranks (stream-ordered): push -> barrier -> routing build and
+ * experts on every rank -> barrier -> pull. */
+/* Stream-ordered barrier across the ranks: flag_bufs[g] = rank g's flag area (bm_ep_flag_bytes() bytes, zeroed once
+ * before the first use, mapped by every rank).  Every rank must enter the barriers of a channel (0..7) in the same
+ * order.  The wait is bounded by limit_ms; when it runs out the kernel returns and bm_layer_status(layer) reports
+ * BM_ERR_TIMEOUT (a rank that never arrives costs a time-out, not a hang). */
+BM_API size_t bm_ep_flag_bytes(void);
+BM_API int bm_ep_barrier(const bm_layer_t* layer, void* const* flag_bufs, int32_t world, int32_t rank, int32_t channel,
+                         int32_t limit_ms, void* stream);
+/* Dispatch: this rank's own slices h_bufs[rank][.][rank] and route_bufs[rank][.][rank] must hold its tokens' rows and
+ * top-k.  Every token's top-k is written to every peer; its two rows only to the peers that own one of its experts. */
+BM_API int bm_ep_push(void* const* h_bufs, void* const* route_bufs, int32_t world, int32_t rank, int32_t T, int32_t r,
+                      int32_t k, int32_t experts_per_rank, void* stream);
+/* Combine: rank_accum fp32 [T, r_out] of this rank's tokens = sum, in ascending rank order, of the partial rows of the
+ * ranks that own one of the token's experts (my_topk_idx int32 [T, k], this rank's own routing). */
+BM_API int bm_ep_pull_reduce(void* const* part_bufs, const int32_t* my_topk_idx, int32_t world, int32_t rank, int32_t T,
+                             int32_t r_out, int32_t k, int32_t experts_per_rank, float* rank_accum, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
