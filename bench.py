@@ -1,16 +1,27 @@
-"""MoE-layer tokens/s on synthetic Qwen3-30B-A3B-shaped layers (decode headline, prefill beside it).
+"""MoE-layer tokens/s on synthetic layers of the benchmark shapes.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload auto|decode|ep]
 
-A step is one forward of one packed MoE layer over one batch of tokens: route -> basis
-projections -> packed experts -> down basis.  The timed loop rotates over `--layers` distinct
-weight sets (more than two L2s of packed bytes) so every step streams its experts from HBM.
-Rank 0 prints one JSON line.  `--impl reference` times the CPU dequantise-then-matmul path on
-the host cores instead (the reference ships no CPU forward; see oracle/cpu_path.py).
+Two workloads, both "one step = one forward of one packed MoE layer over one batch of tokens":
+
+  decode  Qwen3-30B-A3B layer shape (128 experts of 768, top-8, rank-256 shared basis, mixed 2/3/4 bits), 64 tokens:
+          route -> basis projections -> packed experts -> down basis.  The timed loop rotates over --layers distinct
+          weight sets (more than two L2s of packed bytes), so every step streams its experts from HBM.  1 / 8 / 32
+          tokens and the 8192-token Zipf prefill of the same layer are reported beside it.
+  ep      Qwen3-Next-80B-A3B layer shape (512 experts of 512, top-10, gated shared expert), 16384 tokens in total,
+          expert-parallel over the N GPUs (strong scaling: the batch is split over the ranks, experts are sharded,
+          rank-space rows are exchanged through peer memory).  N = 1 is the same layer and batch on one GPU.
+
+--workload auto (the default) picks `ep` when the process is one of several ranks or when several GPUs are visible
+(the run is then one point of a 1/2/4/8-GPU series, which has to be one workload), else `decode`.
+Rank 0 prints one JSON line.  `--impl reference` times the CPU dequantise-then-matmul path of the same workload on
+the host cores instead (the reference ships no CPU forward; oracle/cpu_path.py restates it).
 """
 from __future__ import annotations
 
 import argparse
+import glob
+import importlib.util
 import json
 import os
 import subprocess
@@ -24,8 +35,11 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
-METRIC = "moe_layer_decode_tokens_per_s"
+METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
+# DRAM bytes (read + write) of one launch of the packed-experts kernel at the decode headline (64 tokens, Qwen3-30B-A3B
+# shape), from a profiler capture; valid only for the arena layout version it was captured with.
+DECODE_KERNEL_DRAM_BYTES = {3: None}
 
 
 def parse():
@@ -34,14 +48,15 @@ def parse():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "decode", "ep"])
     ap.add_argument("--tokens", type=int, default=64, help="decode batch of the headline number")
-    ap.add_argument("--layers", type=int, default=12, help="distinct weight sets rotated through")
+    ap.add_argument("--layers", type=int, default=12, help="distinct weight sets rotated through (decode workload)")
     ap.add_argument("--prefill-tokens", type=int, default=8192)
-    ap.add_argument("--no-extras", action="store_true", help="headline only (skip other batch sizes / prefill / cpu)")
+    ap.add_argument("--ep-tokens", type=int, default=16384, help="tokens of one step of the ep workload, over all GPUs")
+    ap.add_argument("--ep-layers", type=int, default=4, help="distinct weight sets rotated through (ep workload)")
+    ap.add_argument("--waves", type=int, default=2, help="ep workload: waves per step and rank (exchange of one beside compute of the other)")
+    ap.add_argument("--no-extras", action="store_true", help="headline only (skip other batch sizes / prefill / cpu / reference kernels)")
     ap.add_argument("--path", type=int, default=0, help="experts path: 0 auto, 1 generic, 2 decode, 3 tensor")
-    ap.add_argument("--parallel", default="dp", choices=["dp", "ep"],
-                    help="with --gpus N > 1: dp = every rank runs the whole layer on its own tokens (weights replicated, "
-                         "no data-path collective); ep = experts sharded over the ranks, rank-space exchange over NCCL")
     ap.add_argument("--probe", default=None, choices=["experts", "forward"],
                     help="no timing: run the packed-experts stage or the whole layer forward --steps times over --layers "
                          "rotating weight sets with --tokens tokens (Zipf(1.1) routing above 256 tokens) and exit; the "
@@ -103,11 +118,44 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def dist_env(args):
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    return rank, world, local
+def dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def pick_workload(args, world):
+    if args.workload != "auto":
+        return args.workload
+    visible = torch.cuda.device_count() if torch.cuda.is_available() else 1
+    return "ep" if (world > 1 or args.gpus > 1 or visible > 1) else "decode"
+
+
+def decode_workload_name(tokens):
+    return (f"qwen3-30b-a3b moe layer decode, {tokens} tokens per GPU, mixed 2/3/4-bit (0.8/0.15/0.05), "
+            "rank-256 shared basis, top-8 of 128 experts")
+
+
+def ep_workload_name(tokens):
+    return (f"qwen3-next-80b-a3b moe layer prefill, {tokens} tokens in total, mixed 2/3/4-bit (0.75/0.2/0.05), rank-256 shared "
+            "basis, top-10 of 512 experts + gated shared expert, expert-parallel")
+
+
+def config_for(workload, args, world):
+    """The `config` object of the JSON line: identical for the GPU arm and the reference arm of one workload."""
+    if workload == "decode":
+        return {"workload": decode_workload_name(args.tokens), "tokens_per_gpu": args.tokens, "layers_rotated": args.layers,
+                "l2": f"inputs larger than L2: {args.layers} distinct weight sets of ~23 MB rotate through the timed loop",
+                "launch": "all timed steps captured in one CUDA graph, replayed once inside the CUDA-event bracket",
+                "parallelism": "1 GPU" if world == 1 else
+                f"dp{world}: every GPU runs the whole layer on its own {args.tokens} tokens, weights replicated, no data-path collective"}
+    per = 512 // world
+    return {"workload": ep_workload_name(args.ep_tokens), "tokens_total": args.ep_tokens, "tokens_per_gpu": args.ep_tokens // world,
+            "waves": args.waves, "layers_rotated": args.ep_layers,
+            "l2": f"inputs larger than L2: every step reads {args.ep_tokens // world} fresh token rows per GPU and rotates over "
+                  f"{args.ep_layers} weight sets",
+            "launch": "eager launches, CUDA events around the timed steps, max over ranks",
+            "parallelism": "1 GPU (all 512 experts local)" if world == 1 else
+            f"ep{world}: {per} experts per GPU, tokens split over the GPUs, rank-space rows pushed to the owners of each token's "
+            "experts and partial rows pulled back through peer memory (NVLink), bounded barriers between the stages"}
 
 
 # ------------------------------------------------------------------------------------------- CPU arm
@@ -126,51 +174,79 @@ def cpu_layer_from(layer, top_k, weight_dtype):
                              top_k, layer.cfg.norm_topk_prob, weight_dtype)
 
 
+def cpu_shared_expert(x, shared):
+    """Dense shared expert(s) on the host cores, fp32 (gated by sigmoid(x . w) where the layer has a gate)."""
+    xf = x.float()
+    y = (torch.nn.functional.silu(xf @ shared["gate"].float().T) * (xf @ shared["up"].float().T)) @ shared["down"].float().T
+    if "gate_logit_w" in shared:
+        y = torch.sigmoid(xf @ shared["gate_logit_w"].float().T) * y
+    return y
+
+
 def time_cpu(layer, tokens, steps, warmup):
+    """tokens/s of the dequantise-then-matmul forward of `layer` on all host cores (dense shared expert included)."""
     from bitsmoe_b200 import synth
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    cl = cpu_layer_from(layer, layer.cfg.top_k, torch.bfloat16)
-    x = synth.activations(layer.cfg, tokens, seed=1)
-    logits = synth.router_logits(layer.cfg, tokens, seed=2)
+    cfg = layer.cfg
+    cl = cpu_layer_from(layer, cfg.top_k, torch.bfloat16 if cfg.round_route_weights else None)
+    shared = None if layer.shared is None else {k: v.cpu() for k, v in layer.shared.items()}
+    x = synth.activations(cfg, tokens, seed=1)
+    logits = synth.router_logits(cfg, tokens, seed=2)
+
+    def step():
+        y = cl.forward(x, logits)
+        if shared is not None:
+            y = y.float() + cpu_shared_expert(x, shared)
+        return y
+
     for _ in range(warmup):
-        cl.forward(x, logits)
+        step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        cl.forward(x, logits)
+        step()
     dt = (time.perf_counter() - t0) / steps
     return tokens / dt, dt, cores
 
 
-def workload_name(tokens):
-    return (f"qwen3-30b-a3b moe layer decode, {tokens} tokens per GPU, mixed 2/3/4-bit (0.8/0.15/0.05), "
-            "rank-256 shared basis, top-8 of 128 experts")
-
-
 def reference_arm(args):
-    rank, world, _ = dist_env(args)
+    rank, world, _ = dist_env()
     if rank != 0:
         return
     from bitsmoe_b200 import synth
-    cfg = synth.QWEN3_30B
+    workload = pick_workload(args, world)
+    if workload == "decode":
+        cfg, tokens, name = synth.QWEN3_30B, args.tokens, decode_workload_name(args.tokens)
+        sample = f"forwards of one layer, {tokens} tokens, dequantise-then-matmul fp32"
+        scaling = "weak"
+    else:
+        # a bounded sample of the 16384-token step: 64 of its tokens through the same layer
+        cfg, tokens, name = synth.QWEN3_NEXT_80B, 64, ep_workload_name(args.ep_tokens)
+        sample = (f"forwards of one layer on a 64-token sample of the {args.ep_tokens}-token step, dequantise-then-matmul "
+                  "fp32, dense shared expert included")
+        scaling = "strong"
     layer = synth.make_layer(cfg, seed=42, device="cpu")
-    steps = max(1, min(args.steps, 20))
-    warm = max(1, min(args.warmup, 2))
-    tps, dt, cores = time_cpu(layer, args.tokens, steps, warm)
+    # honour --steps / --warmup; one CPU step takes 0.3 .. 1 s, so the defaults stay within minutes
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    t_probe = time.perf_counter()
+    tps, dt, cores = time_cpu(layer, tokens, 1, 1)
+    budget = 240.0 - (time.perf_counter() - t_probe)
+    if (steps + warm) * dt > budget:          # never more than ~4 minutes of CPU work, whatever was asked for
+        scale = budget / ((steps + warm) * dt)
+        steps, warm = max(1, int(steps * scale)), max(0, int(warm * scale))
+    tps, dt, cores = time_cpu(layer, tokens, steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.tokens), "tokens_per_gpu": args.tokens,
-                   "sample": "one layer on the host cores of rank 0; the GPU arm's step on the same shapes"},
-        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{steps} forwards of one layer, {args.tokens} tokens, dequantise-then-matmul fp32"},
+        "warmup": warm, "steps_asked": args.steps, "warmup_asked": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_for(workload, args, max(world, args.gpus)),
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": f"{steps} {sample}"},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------------------------------- GPU arm
+# ------------------------------------------------------------------------------------------- GPU helpers
 def timed(fn, steps, stream_sync, use_graph=True, repeats_out=None):
     """CUDA-event time, in ms, of `steps` calls of fn(i).  The calls are captured once into a CUDA graph
     (the launch sequence of all `steps` steps), replayed once untimed and then once inside the timed region, so the
@@ -222,6 +298,17 @@ def active_expert_bytes(packed, offsets_cpu):
     return n, act
 
 
+def load_reference_kernels():
+    """The reference's own extension recompiled for sm_100a (oracle/_ref, built by oracle/build_ref.py), or None."""
+    hits = glob.glob(os.path.join(ROOT, "oracle", "_ref", "_mlp_forward_cuda*.so"))
+    if not hits:
+        return None
+    spec = importlib.util.spec_from_file_location("_mlp_forward_cuda", hits[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def probe(args):
     """Small fixed workload for profiler captures (one GPU): see --probe."""
     from bitsmoe_b200 import synth
@@ -253,42 +340,26 @@ def probe(args):
     print(json.dumps({"probe": args.probe, "tokens": T, "layers": L, "steps": args.steps}), flush=True)
 
 
-def gpu_arm(args):
-    from bitsmoe_b200 import capi, synth
-    from bitsmoe_b200.layer import route_build, route_topk
-    rank, world, local = dist_env(args)
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+def init_dist(dev, world):
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")     # plain peer traffic: no multicast objects on this pool
         dist.init_process_group("nccl", device_id=dev)
+
+
+# ------------------------------------------------------------------------------------------- decode workload
+def decode_arm(args):
+    from bitsmoe_b200 import capi, synth
+    from bitsmoe_b200.layer import route_build, route_topk
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    init_dist(dev, world)
     cfg = synth.QWEN3_30B
     pk = peaks()
+    lib = capi.lib()
     L = args.layers
-    use_ep = world > 1 and args.parallel == "ep"
-    if world > 1:
-        from bitsmoe_b200 import ep
-
-        class _EpAdapter:
-            """Gives an expert-parallel layer the call signature the step functions use."""
-
-            def __init__(self, lyr):
-                self.epl = ep.ExpertParallelPackedLayer(lyr.tables, lyr.vh_gate, lyr.vh_up, lyr.u_down, cfg.intermediate, cfg.rank,
-                                                        cfg.num_experts, cfg.top_k, device=dev)
-                self.num_experts = cfg.num_experts // world
-                self.packed = self.epl.packed
-
-            def forward(self, x, logits, top_k, renorm, wdt, out=None, path=0):
-                y = self.epl.forward(x, logits, wdt, uniform=True)
-                if out is not None:
-                    out.copy_(y)
-                return y
-
-    if use_ep:
-        # every rank generates the same weight sets (same seeds) and keeps only its experts
-        layers = [_EpAdapter(synth.make_layer(cfg, seed=42 + i, device=dev)) for i in range(L)]
-    else:
-        layers = [synth.to_packed_layer(synth.make_layer(cfg, seed=42 + i, device=dev), dev) for i in range(L)]
+    layers = [synth.to_packed_layer(synth.make_layer(cfg, seed=42 + i, device=dev), dev) for i in range(L)]
     sync = lambda: torch.cuda.synchronize(dev)
 
     def barrier():
@@ -297,7 +368,35 @@ def gpu_arm(args):
             torch.distributed.barrier()
             sync()
 
-    def decode_case(T, steps, warmup, want_roofline):
+    def experts_stage(T, steps, zipf=0.0, n_layers=L):
+        """The packed-experts stage alone on prepared routing, same rotation: its time, algorithmic bytes and flops."""
+        prep = []
+        for i in range(n_layers):
+            x = synth.activations(cfg, T, seed=7 + i + 1000 * rank, device=dev)
+            lg = synth.router_logits(cfg, T, seed=9 + i + 1000 * rank, zipf_s=zipf, device=dev)
+            idx, w = route_topk(lg, cfg.top_k, True, torch.bfloat16)
+            tok, off, rw, _, _ = route_build(idx, w, cfg.num_experts)
+            hg, hu = layers[i].basis_project(x)
+            prep.append((hg, hu, tok, off, rw))
+        est = lambda i: layers[i % n_layers].experts_forward(*prep[i % n_layers], path=args.path)
+        for i in range(3):
+            est(i)
+        ems = timed(est, steps, sync) / steps
+        byts, act = 0, 0
+        for i in range(n_layers):
+            b, a = active_expert_bytes(layers[i], prep[i][3].cpu().tolist())
+            byts += b
+            act += a
+        byts = byts / n_layers + T * cfg.rank * 2 * 2 + T * cfg.top_k * 8 + (cfg.num_experts + 1) * 4 + T * cfg.rank * 4
+        return ems, byts, act / n_layers, prep
+
+    def hbm_roofline(ems, byts, act, traffic=None):
+        achieved = byts / (ems * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                "traffic": traffic, "peak_source": pk["source"], "kernel": "packed experts stage (rank_accum clear + experts_decode_kernel)",
+                "kernel_ms": ems, "algorithmic_bytes": byts, "active_experts": act}
+
+    def decode_case(T, steps, warmup, spread):
         # every rank draws its own tokens
         xs = [synth.activations(cfg, T, seed=7 + i + 1000 * rank, device=dev) for i in range(L)]
         lg = [synth.router_logits(cfg, T, seed=9 + i + 1000 * rank, device=dev) for i in range(L)]
@@ -307,35 +406,17 @@ def gpu_arm(args):
             step(i)
         barrier()
         reps = (8, [])
-        ms = timed(step, steps, sync, use_graph=True, repeats_out=reps if want_roofline else None)
-        out = {"tokens": T, "ms_per_step": ms / steps, "tokens_per_s": T * steps / (ms * 1e-3)}
+        n0 = int(lib.bm_launch_count())
+        ms = timed(step, steps, sync, use_graph=True, repeats_out=reps if spread else None)
+        launches = int(lib.bm_launch_count()) - n0       # launches recorded into the graph = launches of one replay
+        out = {"tokens": T, "ms_per_step": ms / steps, "tokens_per_s": T * steps / (ms * 1e-3), "gpu_launches": launches}
         if reps[1]:
             r = sorted(x / steps for x in reps[1])
-            out["ms_per_step_replays"] = {"n": len(r), "p10": r[max(0, int(0.1 * len(r)) )], "p50": r[len(r) // 2], "p90": r[min(len(r) - 1, int(0.9 * len(r)))]}
-        if want_roofline and use_ep:
-            out.update(experts_kernel_ms=None, experts_bytes=None, active_experts=None)
-        elif want_roofline:
-            # dominant kernel alone: the packed-experts stage on prepared routing, same rotation
-            prep = []
-            for i in range(L):
-                idx, w = route_topk(lg[i], cfg.top_k, True, torch.bfloat16)
-                tok, off, rw, _, _ = route_build(idx, w, cfg.num_experts)
-                hg, hu = layers[i].basis_project(xs[i])
-                prep.append((hg, hu, tok, off, rw))
-            est = lambda i: layers[i % L].experts_forward(*prep[i % L], path=args.path)
-            for i in range(3):
-                est(i)
-            ems = timed(est, steps, sync) / steps
-            byts = 0
-            act = 0
-            for i in range(L):
-                b, a = active_expert_bytes(layers[i], prep[i][3].cpu().tolist())
-                byts += b
-                act += a
-            byts = byts / L + T * cfg.rank * 2 * 2 + T * cfg.top_k * 8 + (cfg.num_experts + 1) * 4 + T * cfg.rank * 4
-            out["experts_kernel_ms"] = ems
-            out["experts_bytes"] = byts
-            out["active_experts"] = act / L
+            out["ms_per_step_replays"] = {"n": len(r), "p10": r[max(0, int(0.1 * len(r)))], "p50": r[len(r) // 2],
+                                          "p90": r[min(len(r) - 1, int(0.9 * len(r)))]}
+        ems, byts, act, _ = experts_stage(T, steps)
+        traffic = DECODE_KERNEL_DRAM_BYTES.get(int(lib.bm_arena_layout_version())) if (T == 64 and args.path == 0) else None
+        out["roofline"] = hbm_roofline(ems, byts, act, traffic)
         return out
 
     def e2e_case(T, steps, warmup):
@@ -344,7 +425,7 @@ def gpu_arm(args):
         downloads overlap other steps' kernels as a serving loop would arrange them; steps are handed from stream
         to stream in groups of GROUP (two groups of device buffer sets), because every cross-stream edge of the
         CUDA graph costs a few microseconds.  The whole pipeline is one CUDA graph."""
-        GROUP = int(os.environ.get("BM_E2E_GROUP", "4"))
+        GROUP = 4
         NB = 2 * GROUP
         hx = [synth.activations(cfg, T, seed=70 + i + 1000 * rank).pin_memory() for i in range(4)]
         hl = [synth.router_logits(cfg, T, seed=90 + i + 1000 * rank).pin_memory() for i in range(4)]
@@ -402,7 +483,7 @@ def gpu_arm(args):
     extra = {}
     if not args.no_extras and world == 1:
         for T in (1, 8, 32):
-            extra[f"decode_{T}"] = decode_case(T, args.steps, args.warmup, True)
+            extra[f"decode_{T}"] = decode_case(T, args.steps, args.warmup, False)
         try:
             Tp = args.prefill_tokens
             xs = synth.activations(cfg, Tp, seed=3, device=dev)
@@ -413,104 +494,241 @@ def gpu_arm(args):
                 pstep(i)
             n = max(2, min(args.steps, 5))
             pms = timed(pstep, n, sync) / n
-            flops = Tp * cfg.top_k * 3 * 2 * cfg.rank * cfg.intermediate + Tp * 3 * 2 * cfg.hidden * cfg.rank
-            extra[f"prefill_{Tp}"] = {"tokens": Tp, "ms_per_step": pms, "tokens_per_s": Tp / (pms * 1e-3),
-                                      "tflops": flops / (pms * 1e-3) / 1e12,
-                                      "frac_of_bf16_peak": flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], "router": "zipf 1.1"}
+            flops_experts = Tp * cfg.top_k * 3 * 2 * cfg.rank * cfg.intermediate
+            flops = flops_experts + Tp * 3 * 2 * cfg.hidden * cfg.rank
+            kms, _, _, _ = experts_stage(Tp, n, zipf=1.1, n_layers=min(L, 4))
+            extra[f"prefill_{Tp}"] = {
+                "tokens": Tp, "ms_per_step": pms, "tokens_per_s": Tp / (pms * 1e-3), "tflops": flops / (pms * 1e-3) / 1e12,
+                "frac_of_bf16_peak": flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops"], "router": "zipf 1.1",
+                "roofline": {"bound": "tensor", "achieved": flops_experts / (kms * 1e-3) / 1e12, "peak": pk["bf16_tflops"],
+                             "unit": "TFLOP/s", "frac": flops_experts / (kms * 1e-3) / 1e12 / pk["bf16_tflops"], "traffic": None,
+                             "peak_source": pk["source"], "kernel": "packed experts stage (rank_accum clear + experts_tc_kernel)",
+                             "kernel_ms": kms, "algorithmic_flops": flops_experts}}
         except Exception as ex:  # keep the headline if the large case fails
             extra["prefill_error"] = repr(ex)
-
-    if world > 1 and not use_ep and not args.no_extras:
-        # the same layer expert-parallel (experts sharded over the ranks, rank-space exchange over NCCL): both steps
-        # in CUDA graphs (fixed-size all_gather / reduce_scatter exchange); max over ranks
-        import torch.distributed as dist
+        # the kernels to beat: the reference's own CUDA op, recompiled for sm_100a, at the op boundary on the same inputs
         try:
-            ep_layers = [_EpAdapter(synth.make_layer(cfg, seed=42 + i, device=dev)) for i in range(min(L, 4))]
-            Le = len(ep_layers)
-            T = args.tokens
-            xs = [synth.activations(cfg, T, seed=7 + i + 1000 * rank, device=dev) for i in range(Le)]
-            lg = [synth.router_logits(cfg, T, seed=9 + i + 1000 * rank, device=dev) for i in range(Le)]
-            estep = lambda i: ep_layers[i % Le].forward(xs[i % Le], lg[i % Le], cfg.top_k, True, torch.bfloat16)
-            for i in range(3):
-                estep(i)
-            barrier()
-            n = min(args.steps, 50)
-            ems = timed(estep, n, sync, use_graph=True) / n
-            Tp = args.prefill_tokens
-            xp = synth.activations(cfg, Tp, seed=3 + 1000 * rank, device=dev)
-            lp = synth.router_logits(cfg, Tp, seed=4 + 1000 * rank, device=dev)     # N(0,1): near-uniform expert load
-            pstep = lambda i: ep_layers[i % Le].forward(xp, lp, cfg.top_k, True, torch.bfloat16)
-            for i in range(2):
-                pstep(i)
-            barrier()
-            pms = timed(pstep, 3, sync, use_graph=True) / 3
-            t = torch.tensor([ems, pms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            extra["ep_decode"] = {"tokens_per_gpu": T, "ms_per_step": float(t[0]), "tokens_per_s": world * T / (float(t[0]) * 1e-3)}
-            extra["ep_prefill"] = {"tokens_per_gpu": Tp, "ms_per_step": float(t[1]), "tokens_per_s": world * Tp / (float(t[1]) * 1e-3),
-                                   "router": "N(0,1) logits"}
-            del ep_layers
+            ref = load_reference_kernels()
+            if ref is None:
+                extra["reference_cuda"] = {"unavailable": "oracle/_ref holds no recompiled reference extension"}
+            else:
+                lyr = synth.make_layer(cfg, seed=42, device=dev)
+                lists = []
+                for tag in ("gate", "up", "down"):
+                    for f in ("payload", "rank_idx", "tile_meta", "slab_meta", "scale", "s"):
+                        lists.append([t.to(dev) for t in lyr.tables[tag][f]])
+                rows = {}
+                for T in (1, 8, 32, 64, 2048):
+                    _, _, _, prep = experts_stage(T, 2, zipf=1.1 if T > 256 else 0.0, n_layers=1)
+                    hg, hu, tok, off, rw = prep[0]
+                    call = lambda _i: ref.moe_packed_forward(hg, hu, tok, off, rw, *lists, cfg.rank, cfg.intermediate, 0)
+                    for i in range(3):
+                        call(i)
+                    n = 20 if T <= 64 else 5
+                    rms = timed(call, n, sync, use_graph=False) / n      # the reference op synchronises: no graph
+                    oms = timed(lambda i: layers[0].experts_forward(hg, hu, tok, off, rw, path=args.path), n, sync, use_graph=False) / n
+                    rows[str(T)] = {"reference_op_ms": rms, "this_op_ms": oms, "timing": "eager launches, CUDA events, same inputs"}
+                extra["reference_cuda"] = rows
         except Exception as ex:
-            extra["ep_error"] = repr(ex)
+            extra["reference_cuda"] = {"error": repr(ex)}
 
-    value = head["tokens_per_s"]
-    ms_step = head["ms_per_step"]
+    value, ms_step = head["tokens_per_s"], head["ms_per_step"]
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([ms_step, e2e["value"]], device=dev, dtype=torch.float64)
-        mx = t.clone()
+        mx, mn = t.clone(), t.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        mn = t.clone()
         dist.all_reduce(mn, op=dist.ReduceOp.MIN)
         ms_step = float(mx[0])
         value = world * args.tokens / (ms_step * 1e-3)
         e2e["value"] = float(mn[1]) * world
-    if world > 1:
-        torch.distributed.barrier()
-        torch.distributed.destroy_process_group()
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
-    achieved = head["experts_bytes"] / (head["experts_kernel_ms"] * 1e-3) / 1e9 if not use_ep else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": workload_name(args.tokens),
-                   "tokens_per_gpu": args.tokens, "layers_rotated": L,
-                   "l2": f"inputs larger than L2: {L} distinct weight sets of ~23 MB rotate through the timed loop",
-                   "launch": "all timed steps captured in one CUDA graph, replayed once inside the CUDA-event bracket",
-                   "parallelism": "1 GPU" if world == 1 else
-                   (f"ep{world}: experts sharded over {world} GPUs, rank-space all_gather dispatch / reduce_scatter combine (NCCL), captured in the same CUDA graph"
-                    if use_ep else
-                    f"dp{world}: every GPU runs the whole layer on its own {args.tokens} tokens, weights replicated, no data-path collective")},
-        "e2e": e2e, "gpu_launches": 5 * args.steps, "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": (achieved / pk["hbm_gbs"]) if achieved else None,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch at this workload, from the ncu capture
-                     # summarised in profiles/experts_decode_kernel_qwen3-30b_64tok.md
-                     "traffic": 25056512 if (args.tokens == 64 and args.path == 0 and achieved) else None,
-                     "peak_source": pk["source"],
-                     "kernel": "packed experts stage", "kernel_ms": head["experts_kernel_ms"],
-                     "algorithmic_bytes": head["experts_bytes"], "active_experts": head["active_experts"]},
-        "extra": extra,
+        "config": config_for("decode", args, world),
+        "e2e": e2e, "gpu_launches": head["gpu_launches"], "clocks": clocks, "roofline": head["roofline"], "extra": extra,
     }
     if "ms_per_step_replays" in head:
         line["ms_per_step_replays"] = head["ms_per_step_replays"]
     if not args.no_extras and world == 1:
-        cpu_layer = synth.make_layer(cfg, seed=42, device=dev)
-        cpu_layer.tables = {t: {f: [x.cpu() for x in v] for f, v in fl.items()} for t, fl in cpu_layer.tables.items()}
+        cpu_layer = synth.make_layer(cfg, seed=42, device="cpu")
         tps, dt, cores = time_cpu(cpu_layer, args.tokens, 3, 1)
         line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": f"3 forwards of one layer, {args.tokens} tokens, dequantise-then-matmul fp32 "
+                                          f"({dt * 1e3:.0f} ms each)"}
+        # the CPU-runnable configuration of the specification: DeepSeek-V2-Lite shape, uniform 2-bit, 64 tokens,
+        # two shared experts (a dense MLP of width 2816), through the same dequantise-then-matmul path
+        ds = synth.make_layer(synth.DEEPSEEK_V2_LITE, seed=42, device="cpu")
+        tps, dt, cores = time_cpu(ds, 64, 3, 1)
+        line["extra"]["cpu_baseline_deepseek_v2_lite"] = {
+            "value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"3 forwards of one deepseek-v2-lite-shaped layer (64 experts of 1408, top-6, 2-bit, shared experts), "
+                      f"64 tokens ({dt * 1e3:.0f} ms each)"}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------- ep workload
+def ep_arm(args):
+    """Strong scaling of one Qwen3-Next-80B-A3B-shaped layer over the ranks: see the module docstring."""
+    from bitsmoe_b200 import capi, ep, synth
+    from bitsmoe_b200.layer import PackedLayer
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    init_dist(dev, world)
+    import torch.distributed as dist
+    cfg = synth.QWEN3_NEXT_80B
+    pk = peaks()
+    lib = capi.lib()
+    total = args.ep_tokens
+    if total % (world * args.waves):
+        raise SystemExit(f"--ep-tokens {total} must be a multiple of gpus * waves = {world * args.waves}")
+    T_loc = total // world
+    L = args.ep_layers
+    sync = lambda: torch.cuda.synchronize(dev)
+
+    def barrier():
+        sync()
+        if world > 1:
+            dist.barrier()
+            sync()
+
+    # every rank generates the same weight sets (same seeds) and keeps only its experts
+    synth_layers = [synth.make_layer(cfg, seed=42 + i, device=dev) for i in range(L)]
+    shared = [{k: v.to(dev, torch.bfloat16) for k, v in s.shared.items()} for s in synth_layers]
+
+    def local_layer(s):
+        t = ep.shard_tables(s.tables, rank, world)
+        return PackedLayer(t["gate"], t["up"], t["down"], cfg.intermediate, cfg.rank, s.vh_gate, s.vh_up, s.u_down, device=dev)
+
+    packed = [local_layer(s) for s in synth_layers]
+    sym = [ep.SymmetricExpertParallel(p, cfg.num_experts, cfg.top_k, T_loc // args.waves, cfg.norm_topk_prob) for p in packed] \
+        if world > 1 else None
+
+    def shared_expert(x, sh):
+        """sigmoid(x . w_g) * MLP(x) of the gated shared expert: dense bf16 (library GEMMs), added as the residual."""
+        y = (torch.nn.functional.silu(x @ sh["gate"].T) * (x @ sh["up"].T)) @ sh["down"].T
+        return torch.sigmoid(x @ sh["gate_logit_w"].T) * y
+
+    xs = [synth.activations(cfg, T_loc, seed=7 + i + 1000 * rank, device=dev) for i in range(L)]
+    lg = [synth.router_logits(cfg, T_loc, seed=9 + i + 1000 * rank, device=dev) for i in range(L)]
+    ys = [torch.empty_like(xs[0]) for _ in range(L)]
+
+    def step(i):
+        j = i % L
+        res = shared_expert(xs[j], shared[j])
+        if world == 1:
+            packed[j].forward(xs[j], lg[j], cfg.top_k, cfg.norm_topk_prob, torch.bfloat16, residual=res, out=ys[j], path=args.path)
+        else:
+            sym[j].forward(xs[j], lg[j], torch.bfloat16, residual=res, out=ys[j], overlap=args.waves > 1)
+        return ys[j]
+
+    # on-box parity of the expert-parallel step: rank 0 runs its own tokens through the whole layer on one GPU
+    parity = None
+    if world > 1:
+        y_ep = step(0).float().clone()
+        sync()
+        if rank == 0:
+            full = synth.to_packed_layer(synth_layers[0], dev)
+            y_one = full.forward(xs[0], lg[0], cfg.top_k, cfg.norm_topk_prob, torch.bfloat16,
+                                 residual=shared_expert(xs[0], shared[0])).float()
+            sync()
+            err = (y_ep - y_one)
+            parity = {"max_abs_err": float(err.abs().max()), "max_abs_ref": float(y_one.abs().max()),
+                      "rel_l2": float(err.norm() / y_one.norm()), "tokens_checked": T_loc,
+                      "against": "the same layer with all 512 experts on one GPU, same tokens of rank 0"}
+            parity["ok"] = bool(parity["max_abs_err"] <= 2e-2 * parity["max_abs_ref"] and parity["rel_l2"] <= 1e-2)
+            del full
+        barrier()
+
+    steps, warm = max(1, args.steps), max(3, args.warmup)
+    with ClockSampler(local) as clk:
+        for i in range(warm):
+            step(i)
+        barrier()
+        n0 = int(lib.bm_launch_count())
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            step(i)
+        stop.record()
+        sync()
+        ms = start.elapsed_time(stop) / steps
+        launches = int(lib.bm_launch_count()) - n0
+        # end to end: the step's inputs come from pinned host memory and its result goes back, every step
+        hx = [x.cpu().pin_memory() for x in xs[:2]]
+        hl = [l.cpu().pin_memory() for l in lg[:2]]
+        hy = torch.empty(xs[0].shape, dtype=xs[0].dtype).pin_memory()
+
+        def e2e_step(i):
+            xs[i % L].copy_(hx[i % 2], non_blocking=True)
+            lg[i % L].copy_(hl[i % 2], non_blocking=True)
+            hy.copy_(step(i), non_blocking=True)
+
+        for i in range(2):
+            e2e_step(i)
+        barrier()
+        start.record()
+        n_e2e = max(1, min(steps, 20))
+        for i in range(n_e2e):
+            e2e_step(i)
+        stop.record()
+        sync()
+        ms_e2e = start.elapsed_time(stop) / n_e2e
+    clocks = clk.summary()
+    for p in packed:
+        p.check_status()
+    nv = None
+    if world > 1:
+        idx, _ = packed[0].route_topk(lg[0][: T_loc // args.waves], cfg.top_k, cfg.norm_topk_prob, torch.bfloat16)
+        push, pull = sym[0].nvlink_bytes_per_wave(idx)
+        nv = {"pushed_per_rank_per_step": push * args.waves, "pulled_per_rank_per_step": pull * args.waves,
+              "estimate": "rows once per (token, destination rank): 2r fp16 out, r_out fp32 back, top-k ids and weights to every rank"}
+        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    flops_experts = total * cfg.top_k * 3 * 2 * cfg.rank * cfg.intermediate
+    flops = flops_experts + total * 3 * 2 * cfg.hidden * cfg.rank + total * 3 * 2 * cfg.hidden * cfg.shared_intermediate
+    tf_per_gpu = flops / (ms * 1e-3) / 1e12 / world
+    line = {
+        "metric": METRIC, "value": total / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warm,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": config_for("ep", args, world),
+        "e2e": {"value": total / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": xs[0].numel() * 2 + lg[0].numel() * 4,
+                "d2h_bytes_per_step": xs[0].numel() * 2, "overlap": "copies on the compute stream (per rank)"},
+        "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": tf_per_gpu, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": tf_per_gpu / pk["bf16_tflops_sustained"], "traffic": None, "peak_source": pk["source"] + " (sustained)",
+                     "kernel": "whole step per GPU (algorithmic flops of routed experts + basis products + shared expert)",
+                     "kernel_ms": ms, "algorithmic_flops": flops},
+        "extra": {"ep_parity": parity, "nvlink_bytes": nv},
+    }
+    if world == 1 and not args.no_extras:
+        cpu_layer = synth.make_layer(cfg, seed=42, device="cpu")
+        tps, dt, cores = time_cpu(cpu_layer, 64, 3, 1)
+        line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"3 forwards of one layer on a 64-token sample of the step, dequantise-then-matmul fp32 "
                                           f"({dt * 1e3:.0f} ms each)"}
     print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
     a = parse()
+    _, _world, _ = dist_env()
     if a.impl == "reference":
         reference_arm(a)
     elif a.probe:
         probe(a)
+    elif pick_workload(a, _world) == "ep":
+        ep_arm(a)
     else:
-        gpu_arm(a)
+        decode_arm(a)

@@ -54,6 +54,8 @@ class LayerDesc(C.Structure):
 
 _SIGS = {
     "bm_abi_version": (C.c_int, []),
+    "bm_launch_count": (C.c_uint64, []),
+    "bm_arena_layout_version": (C.c_int, []),
     "bm_last_error": (C.c_char_p, []),
     "bm_status_string": (C.c_char_p, [C.c_int]),
     "bm_pack_bitplanes_i8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),

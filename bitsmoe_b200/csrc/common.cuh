@@ -22,6 +22,7 @@ constexpr int N_MICRO = 32;    // columns per bit-plane word
 constexpr int MICROS = N_TILE / N_MICRO;
 
 int set_error(int status, const char* fmt, ...);
+void count_launch();   // every kernel launch of the library is counted (bm_launch_count)
 
 #define BM_REQUIRE(cond, status, ...)                       \
   do {                                                      \
@@ -37,6 +38,7 @@ int set_error(int status, const char* fmt, ...);
 
 #define BM_LAUNCH_CHECK(name)                                                              \
   do {                                                                                     \
+    ::bm::count_launch();                                                                  \
     cudaError_t _e = cudaGetLastError();                                                   \
     if (_e != cudaSuccess)                                                                 \
       return ::bm::set_error(BM_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \

@@ -19,6 +19,9 @@ int set_error(int status, const char* fmt, ...) {
   return status;
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 // from the other translation units
 int launch_gemm_nt(const GemmArgs& g, int problems, cudaStream_t st);
 struct SkinnyArgs {
@@ -260,6 +263,8 @@ using namespace bm;
 
 extern "C" int bm_abi_version(void) { return 2; }
 extern "C" const char* bm_last_error(void) { return g_err; }
+extern "C" uint64_t bm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+extern "C" int bm_arena_layout_version(void) { return 3; }   // 3: one contiguous [scales | words] section per matrix and tile
 extern "C" const char* bm_status_string(int s) {
   switch (s) {
     case BM_OK: return "ok";

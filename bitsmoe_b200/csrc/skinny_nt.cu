@@ -254,6 +254,7 @@ int launch_skinny_nt(SkinnyArgs a, cudaStream_t st) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  count_launch();
   BM_CUDA(cudaLaunchKernelEx(&cfg, skinny_nt_kernel, a));
   return BM_OK;
 }

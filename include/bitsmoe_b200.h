@@ -43,6 +43,11 @@ enum { BM_GATE = 0, BM_UP = 1, BM_DOWN = 2 };
 
 BM_API int bm_abi_version(void);
 BM_API const char* bm_last_error(void);
+/* Kernel launches issued by this library in this process so far (a launch recorded into a CUDA graph during stream
+ * capture counts once, when it is captured), and the version of the arena layout that bm_layer_create builds
+ * (recorded profiler captures are only comparable within one version). */
+BM_API uint64_t bm_launch_count(void);
+BM_API int bm_arena_layout_version(void);
 BM_API const char* bm_status_string(int status);
 
 /* ---- bit-plane codec ---------------------------------------------------

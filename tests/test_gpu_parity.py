@@ -171,22 +171,16 @@ def test_experts_forward_q30_shape_vs_oracle_and_reference(q30_small, T):
     helpers.assert_close(got, o["rank_accum"], rtol=1e-3, atol=1e-5, what="rank_accum vs fp32 oracle")
     ref = helpers.load_reference_ext("_mlp_forward_cuda")
     if ref is not None:
-        # The reference's kernels, recompiled for sm_100a, are not run-to-run stable on a B200: in about one
-        # run in four a handful of elements (16 of 16384) came back off by up to 0.016 while the fp32 oracle
-        # and this build agreed.  Compare against the best of three runs of the reference.
+        # The reference's kernels, recompiled for sm_100a, are not run-to-run stable on a B200 (single calls return a few
+        # token rows off while the fp32 oracle and this build agree): the element-wise median of five calls is the
+        # reference value.
         ref_lists = helpers.ref_args(layer, DEV)
-        last = None
-        for _ in range(6):
-            want = ref.moe_packed_forward(*args, *ref_lists, layer.cfg.rank, layer.cfg.intermediate, 0)
+        outs = []
+        for _ in range(5):
+            outs.append(ref.moe_packed_forward(*args, *ref_lists, layer.cfg.rank, layer.cfg.intermediate, 0).float().clone())
             torch.cuda.synchronize()
-            try:
-                helpers.assert_close(want, o["rank_accum"], what="reference kernels vs fp32 oracle")
-                last = None
-                break
-            except AssertionError as exc:
-                last = exc
-        if last is not None:
-            raise last
+        want = torch.stack(outs).median(dim=0).values
+        helpers.assert_close(want, o["rank_accum"], what="reference kernels vs fp32 oracle")
         helpers.assert_close(got, want, what="rank_accum vs the reference's kernels")
 
 

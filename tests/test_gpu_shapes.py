@@ -92,23 +92,17 @@ def _check_stage(layer, packed, experts, args, idx, w, path, tag, rtol, atol):
     run_ref = _reference_rank_accum(layer, args)
     if run_ref is not None:
         # The recompiled reference kernels are not run-to-run stable on this GPU on their tensor-core path (32 tokens
-        # and more): the first calls after a change of shape return whole token rows off by up to 30 % of the peak,
-        # later calls agree with the fp32 oracle to 4e-4 relative L2.  Accept the first of six calls that agrees.
-        last = None
-        for _ in range(6):
-            ref_out = run_ref()
+        # and more): single calls return whole token rows off by up to 30 % of the peak, in different rows from call
+        # to call, while most calls agree with the fp32 oracle to 4e-4 relative L2.  The element-wise median of five
+        # calls is the reference value.  Both sides round their operands to fp16 in different places: element-wise the
+        # specification's tolerance (rtol 2e-2 / atol 1e-2); what makes the comparison sharp are assert_close's
+        # bounds relative to the peak (2e-2) and in L2 (1e-2).
+        outs = []
+        for _ in range(5):
+            outs.append(run_ref().float().clone())
             torch.cuda.synchronize()
-            try:
-                # both sides round their operands to fp16 in different places and the reference adds run-to-run noise
-                # of its own: element-wise the specification's tolerance (rtol 2e-2 / atol 1e-2); what makes the
-                # comparison sharp are assert_close's bounds relative to the peak (2e-2) and in L2 (1e-2)
-                helpers.assert_close(got, ref_out, what=f"{tag}: fast path vs the reference's kernels")
-                last = None
-                break
-            except AssertionError as exc:
-                last = exc
-        if last is not None:
-            raise last
+        ref_out = torch.stack(outs).median(dim=0).values
+        helpers.assert_close(got, ref_out, what=f"{tag}: fast path vs the reference's kernels (median of five calls)")
 
 
 @pytest.mark.parametrize("T", [1, 8, 32, 64])
