@@ -21,20 +21,6 @@
 
 namespace bm {
 
-// Optional per-role phase timing (debug builds): cycles accumulated into status[8 + 2*slot] as uint64.
-#ifdef BM_TC_TIMING
-#define XT_TICK_INIT() long long xt_t_ = clock64()
-#define XT_TICK(slot)                                                                                  \
-  do {                                                                                                 \
-    const long long now_ = clock64();                                                                  \
-    atomicAdd(reinterpret_cast<unsigned long long*>(status + 8) + (slot), static_cast<unsigned long long>(now_ - xt_t_)); \
-    xt_t_ = now_;                                                                                      \
-  } while (0)
-#else
-#define XT_TICK_INIT() do {} while (0)
-#define XT_TICK(slot) do {} while (0)
-#endif
-
 constexpr int XT_NT = 64;                 // tokens (assignments) per item = MMA N
 constexpr int XT_THREADS = 576;
 constexpr int XT_EPI_WARPS = 8, XT_PRODUCER_WARP = 8, XT_MMA_WARP = 9, XT_DQ_WARP0 = 10, XT_DQ_WARPS = 8;
@@ -307,9 +293,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
     } else if (warp == XT_MMA_WARP) {
       // ------------------------------------------------------------------ MMA issue
       if (lane == 0) {
-        XT_TICK_INIT();
         bool ok = xt_wait(&bars.act_ready, item_round & 1, abort_flag);
-        XT_TICK(0);
         uint32_t ri = ring_i, gr = gu_round;
         const uint32_t act_base = tc::smem_u32(sm.act), z_base = tc::smem_u32(sm.z), ring_base = tc::smem_u32(sm.ring);
         const uint32_t act_m_bytes = static_cast<uint32_t>(max_slots / 8) * XT_CHUNK_STRIDE;
@@ -319,7 +303,6 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         const uint64_t z_desc0 = tc::smem_desc_kmajor(z_base, XT_CHUNK_STRIDE, 128);
         for (int tile = 0; tile < n_tiles && ok; ++tile, ++gr) {
           if (gr > 0) ok = xt_wait(&bars.tmem_gu_free, (gr - 1) & 1, abort_flag);
-          XT_TICK(1);
           for (int m = 0; m < 2 && ok; ++m) {
             const int nkb = fe.m[m].nslots >> 4;
             const uint64_t bm_desc = b_desc0 + ((m * act_m_bytes) >> 4);
@@ -337,10 +320,8 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
             }
           }
           if (!ok) break;
-          XT_TICK(2);
           tc::mma_commit(&bars.gu_done);
           ok = xt_wait(&bars.z_ready, gr & 1, abort_flag);
-          XT_TICK(3);
           for (int mt = 0; mt < n_mt && ok; ++mt) {
             for (int kb0 = 0; kb0 < 8; kb0 += XT_STAGE_BLOCKS, ++ri) {
               const int slot = ri % XT_RING;
@@ -355,14 +336,12 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
             }
           }
           if (ok) tc::mma_commit(&bars.down_done);
-          XT_TICK(4);
         }
       }
     }
     else if (warp >= XT_DQ_WARP0) {
       // ------------------------------------------------------------------ dequantisers
       const int dw = warp - XT_DQ_WARP0;
-      XT_TICK_INIT();
       // Two teams of four warps take alternate stages (two pairs of 16-blocks x 128 operand rows); inside a team
       // warp `wt` converts the operand-row blocks x = wt and wt + 4, so two stages are always in flight.
       const int team = dw >> 2, wt = dw & 3, g = lane >> 2, t = lane & 3;
@@ -472,7 +451,6 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
       const uint32_t lane_sel = static_cast<uint32_t>(32 * q) << 16;
       uint32_t gr = gu_round;
       bool ok = true;
-      XT_TICK_INIT();
       const int c = 32 * q + lane;                                   // row of D_g / D_u = column of the tile
       const int c_pos = slot_pos(c);
       unsigned char* zrow = sm.z + (c_pos >> 3) * XT_CHUNK_STRIDE + (c_pos & 7) * 2;
@@ -480,7 +458,6 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         ok = xt_wait(&bars.gu_done, gr & 1, abort_flag, 200);
         if (ok && gr > 0) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag, 200);
         if (!ok) break;
-        if (threadIdx.x == 0) XT_TICK(9);
         tc::fence_after_sync();
         {
           const int n0 = nhalf;
@@ -498,10 +475,8 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         tc::fence_async_smem();
         __syncwarp();
         if (lane == 0) { tc::mbar_arrive(&bars.tmem_gu_free); tc::mbar_arrive(&bars.z_ready); }
-        if (threadIdx.x == 0) XT_TICK(10);
       }
       if (ok) ok = xt_wait(&bars.down_done, (gr - 1) & 1, abort_flag, 200);
-      if (threadIdx.x == 0) XT_TICK(11);
       if (ok) {
         tc::fence_after_sync();
         const FastMat& fd = fe.m[2];
@@ -528,7 +503,6 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         }
         tc::fence_before_sync();
       }
-      if (threadIdx.x == 0) XT_TICK(12);
     }
     // every role advances the shared counters identically
     gu_round += n_tiles;

@@ -89,27 +89,30 @@ def ref_args(layer: synth.SynthLayer, device) -> list:
 
 
 def assert_close(got: torch.Tensor, want: torch.Tensor, rtol: float = RTOL, atol: float = ATOL, what: str = "",
-                 rel_max: float = 2e-2, rel_l2: float = 1e-2) -> None:
+                 rel_max: float = 2e-2, rel_l2: float = 1e-2, outlier_frac: float = 0.0) -> None:
     """Element-wise ``|err| <= atol + rtol*|want|`` AND two bounds relative to the size of the expected signal:
     ``max|err| <= rel_max * max|want|`` and ``||err||_2 <= rel_l2 * ||want||_2``.  The synthetic layers produce
     outputs of order 1e-3 .. 1e-2, far below the absolute tolerance of the specification, so the element-wise test
-    alone would accept an all-zero result; the relative bounds are what makes a wrong kernel fail."""
+    alone would accept an all-zero result; the relative bounds are what makes a wrong kernel fail.
+    ``outlier_frac`` (only for comparisons against a reference that is itself noisy) lets that fraction of the
+    elements violate the element-wise and peak bounds; the L2 bound always covers every element."""
     got, want = got.detach().double().cpu(), want.detach().double().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} != {tuple(want.shape)}"
     assert bool(torch.isfinite(got).all()), f"{what}: non-finite values"
-    err = (got - want).abs()
-    bound = atol + rtol * want.abs()
-    bad = err > bound
-    assert not bool(bad.any()), (f"{what}: {int(bad.sum())}/{bad.numel()} outside rtol={rtol} atol={atol}; "
-                                 f"max abs err {float(err.max()):.4g}, max |want| {float(want.abs().max()):.4g}")
     if want.numel() == 0:
         return
+    err = (got - want).abs()
     peak = float(want.abs().max())
+    allowed = int(outlier_frac * want.numel())
+    bad = err > atol + rtol * want.abs()
+    assert int(bad.sum()) <= allowed, (f"{what}: {int(bad.sum())}/{bad.numel()} outside rtol={rtol} atol={atol}; "
+                                       f"max abs err {float(err.max()):.4g}, max |want| {peak:.4g}")
     if peak == 0.0:
         assert float(err.max()) == 0.0, f"{what}: expected exact zeros, max |got| {float(got.abs().max()):.4g}"
         return
-    assert float(err.max()) <= rel_max * peak, (f"{what}: max abs err {float(err.max()):.4g} > {rel_max} * max|want| "
-                                                f"({peak:.4g})")
+    over = int((err > rel_max * peak).sum())
+    assert over <= allowed, (f"{what}: {over} elements with abs err > {rel_max} * max|want| ({peak:.4g}); "
+                             f"max abs err {float(err.max()):.4g}")
     l2 = float(torch.linalg.vector_norm(got - want)) / float(torch.linalg.vector_norm(want))
     assert l2 <= rel_l2, f"{what}: relative L2 error {l2:.4g} > {rel_l2}"
 
