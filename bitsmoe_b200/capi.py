@@ -69,6 +69,10 @@ _SIGS = {
     "bm_layer_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "bm_layer_set_option": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
     "bm_layer_selftest_wait": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "bm_gate_logits": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int, C.c_void_p]),
+    "bm_dense_mlp_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "bm_dense_mlp_forward": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                       C.c_int32, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
     "bm_ep_flag_bytes": (C.c_size_t, []),
     "bm_ep_barrier": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "bm_ep_push": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),

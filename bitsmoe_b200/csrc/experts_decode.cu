@@ -137,7 +137,7 @@ __device__ __forceinline__ void dense_afrag(uint32_t w, uint32_t (&a)[4]) {
 template <bool DENSE>
 __device__ __forceinline__ void mma_pairs(const uint32_t* __restrict__ wp, int stride, int npairs, const __half* __restrict__ bp,
                                           float (&acc)[4]) {
-#pragma unroll 4
+#pragma unroll 2
   for (int p = 0; p < npairs; ++p) {
     const uint4 b = *reinterpret_cast<const uint4*>(bp);
     uint32_t a[4];
@@ -210,6 +210,9 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// MAXMB: 16-slot blocks of the down matrix per warp (2: up to 256 slots, 4: up to 512); the smaller instance keeps the
+// kernel's code, which the instruction cache has to hold, short.
+template <int MAXMB>
 __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(const DecParams P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ DecUnitInfo info[2];
@@ -473,9 +476,9 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(const DecPa
     consumer_sync();
     if (*abort_flag) break;
 
-    float dtot[DEC_MAX_MB][4];
+    float dtot[MAXMB][4];
 #pragma unroll
-    for (int i = 0; i < DEC_MAX_MB; ++i)
+    for (int i = 0; i < MAXMB; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) dtot[i][j] = 0.f;
     const FastMat& fd = fe.m[2];
@@ -573,7 +576,7 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(const DecPa
             zsum[h] = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
           }
 #pragma unroll
-          for (int i2 = 0; i2 < DEC_MAX_MB; ++i2) {
+          for (int i2 = 0; i2 < MAXMB; ++i2) {
             const int mb = warp + 8 * i2;
             if (mb < nblk_d) {
               float dacc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -612,7 +615,7 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(const DecPa
       const int16_t* rank_d = reinterpret_cast<const int16_t*>(tab);
       const __half* s_d = reinterpret_cast<const __half*>(tab + fd.nslots * 2);
 #pragma unroll
-      for (int i2 = 0; i2 < DEC_MAX_MB; ++i2) {
+      for (int i2 = 0; i2 < MAXMB; ++i2) {
         const int mb = warp + 8 * i2;
         if (mb < nblk_d) {
 #pragma unroll
@@ -648,8 +651,10 @@ int plan_experts_decode(bm_layer* L) {
   BM_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   BM_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
   BM_CUDA(cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev));
+  const bool small = L->max_slots <= 128 * 2;
+  const void* kernel = small ? reinterpret_cast<const void*>(experts_decode_kernel<2>) : reinterpret_cast<const void*>(experts_decode_kernel<DEC_MAX_MB>);
   cudaFuncAttributes fa;
-  BM_CUDA(cudaFuncGetAttributes(&fa, experts_decode_kernel));
+  BM_CUDA(cudaFuncGetAttributes(&fa, kernel));
   const int sec = dec_sec_bytes(L->max_slots, L->max_words);
   const int stat = static_cast<int>(fa.sharedSizeBytes);
   // candidates, best first: (CTAs per SM, operand buffers, ring slots).  More resident warps hide more latency; a ring
@@ -678,10 +683,10 @@ int plan_experts_decode(bm_layer* L) {
     }
   }
   if (pick < 0) return BM_OK;
-  BM_CUDA(cudaFuncSetAttribute(experts_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin - stat));
-  BM_CUDA(cudaFuncSetAttribute(experts_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+  BM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin - stat));
+  BM_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
   int blocks = 0;
-  BM_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, experts_decode_kernel, DEC_THREADS, smem));
+  BM_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, DEC_THREADS, smem));
   if (blocks < 1) return BM_OK;
   L->dec_sec_bytes = sec;
   L->dec_smem = smem;
@@ -722,7 +727,8 @@ int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half*
   P.ring = L->dec_ring;
   P.act_bufs = L->dec_act_bufs;
   P.wait_limit_ns = tc::WAIT_LIMIT_NS;
-  experts_decode_kernel<<<L->dec_grid, DEC_THREADS, L->dec_smem, st>>>(P);
+  if (L->max_slots <= 128 * 2) experts_decode_kernel<2><<<L->dec_grid, DEC_THREADS, L->dec_smem, st>>>(P);
+  else experts_decode_kernel<DEC_MAX_MB><<<L->dec_grid, DEC_THREADS, L->dec_smem, st>>>(P);
   BM_LAUNCH_CHECK("experts_decode_kernel");
   return BM_OK;
 }

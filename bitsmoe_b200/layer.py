@@ -259,3 +259,41 @@ def route_build(topk_idx: torch.Tensor, topk_w: torch.Tensor, num_local: int,
                                       tile_rows, tok.data_ptr(), off.data_ptr(), rw.data_ptr(), tiles.data_ptr(),
                                       counts.data_ptr(), capi.ptr(ws), need, capi.stream_ptr(dev)))
     return tok, off, rw, tiles, counts
+
+
+def gate_logits(x: torch.Tensor, gate_weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Router logits x @ gate_weight.T on the library's kernels: x [T, H] (fp16 / bf16 / fp32), gate_weight fp16 [E, H]
+    -> [T, E] in ``out_dtype`` (default: x's dtype, as ``self.gate(hidden_states)`` gives in the reference)."""
+    if not x.is_cuda:
+        raise RuntimeError("gate_logits requires CUDA tensors; there is no CPU path")
+    x = x.contiguous()
+    w = _as(gate_weight.detach(), torch.float16, x.device)
+    out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        capi.check(capi.lib().bm_gate_logits(x.data_ptr(), capi.dtype_code(x.dtype), w.data_ptr(), x.shape[0], w.shape[0],
+                                             w.shape[1], out.data_ptr(), capi.dtype_code(out.dtype), capi.stream_ptr(x.device)))
+    return out
+
+
+def dense_mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+              token_gate_weight: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Dense SwiGLU MLP of a shared expert on the library's kernels: (silu(x Wg^T) * (x Wu^T)) Wd^T, scaled per token by
+    sigmoid(x . token_gate_weight) when that is given, plus ``residual``.  Weights fp16; result in x's dtype."""
+    if not x.is_cuda:
+        raise RuntimeError("dense_mlp requires CUDA tensors; there is no CPU path")
+    x = x.contiguous()
+    dev = x.device
+    wg, wu, wd = (_as(w.detach(), torch.float16, dev) for w in (w_gate, w_up, w_down))
+    tg = None if token_gate_weight is None else _as(token_gate_weight.detach().reshape(-1), torch.float16, dev)
+    T, H, I = x.shape[0], x.shape[1], wg.shape[0]
+    y = torch.empty_like(x)
+    if residual is not None:
+        residual = residual.to(x.dtype).contiguous()
+    lib = capi.lib()
+    need = int(lib.bm_dense_mlp_workspace_bytes(T, I))
+    ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(lib.bm_dense_mlp_forward(x.data_ptr(), capi.dtype_code(x.dtype), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(),
+                                            capi.ptr(tg), T, H, I, capi.ptr(residual), y.data_ptr(), capi.dtype_code(y.dtype),
+                                            ws.data_ptr(), ws.numel(), capi.stream_ptr(dev)))
+    return y

@@ -225,6 +225,33 @@ class BitsMoE_BaseSparseMoeBlock(nn.Module):
                                "python fallback is intentionally disabled.")
         return self._packed_forward_cuda(h_gate_proj, h_up_proj, token_indices, expert_offsets_t, route_flat, token_count)
 
+    # ---- dense modules of the block on the library's kernels --------------------------------------------
+    @staticmethod
+    def _plain_linear(m) -> bool:
+        return isinstance(m, nn.Linear) and m.bias is None
+
+    def _library_gate_logits(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """x @ gate.weight.T by the library when the gate is a bias-free Linear on the GPU (inference), else None."""
+        gate = getattr(self, "gate", None)
+        if not (x.is_cuda and self._plain_linear(gate) and not torch.is_grad_enabled()):
+            return None
+        from bitsmoe_b200.layer import gate_logits
+        return gate_logits(x, gate.weight)
+
+    def _library_dense_mlp(self, x: torch.Tensor, mlp, token_gate=None) -> Optional[torch.Tensor]:
+        """SwiGLU MLP ``mlp`` (gate_proj / up_proj / down_proj, bias-free, SiLU) by the library, scaled per token by
+        sigmoid(token_gate(x)) when a one-output bias-free Linear is given; None when the module is of another kind."""
+        parts = [getattr(mlp, n, None) for n in ("gate_proj", "up_proj", "down_proj")]
+        if not (x.is_cuda and all(self._plain_linear(p) for p in parts) and not torch.is_grad_enabled()):
+            return None
+        if token_gate is not None and not (self._plain_linear(token_gate) and token_gate.weight.shape[0] == 1):
+            return None
+        if parts[0].weight.shape[0] % 2:
+            return None
+        from bitsmoe_b200.layer import dense_mlp
+        return dense_mlp(x, parts[0].weight, parts[1].weight, parts[2].weight,
+                         None if token_gate is None else token_gate.weight)
+
     # ---- fused path -----------------------------------------------------------------------------------
     def _require_fused(self, x: torch.Tensor):
         if self.shared_vh_gate_proj.numel() == 0 or self.shared_vh_up_proj.numel() == 0:

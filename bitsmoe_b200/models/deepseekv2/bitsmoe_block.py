@@ -59,7 +59,9 @@ class BitsMoE_DeepSeekSparseMoeBlock(BitsMoE_BaseSparseMoeBlock):
         w = topk_weight.reshape(-1, topk_weight.shape[-1]).to(torch.float32)   # not rounded through x.dtype
         residual = None
         if getattr(self.config, "n_shared_experts", None) is not None and hasattr(self, "shared_experts"):
-            residual = self.shared_experts(hidden_states).reshape(-1, orig_shape[-1])
+            residual = self._library_dense_mlp(x, self.shared_experts)
+            if residual is None:
+                residual = self.shared_experts(hidden_states).reshape(-1, orig_shape[-1])
         if self._super_expert_items:
             dense = torch.zeros_like(x)
             self._run_super_experts(x, dense, idx.reshape(-1).long(), self._get_flat_token_ids(x.shape[0], x.device),

@@ -42,7 +42,9 @@ class BitsMoE_Qwen3MoeSparseMoeBlock(BitsMoE_BaseSparseMoeBlock):
         batch, seq, hidden = hidden_states.shape
         x = hidden_states.reshape(-1, hidden)
         self._ensure_runtime_cache(x.device)
-        router_logits = self.gate(x)
+        router_logits = self._library_gate_logits(x)
+        if router_logits is None:
+            router_logits = self.gate(x)
         residual = self._shared_contribution(x)
         if self._super_expert_items:
             # dense (unquantised) experts need the selection on the torch side as well

@@ -36,5 +36,8 @@ class BitsMoE_Qwen3NextSparseMoeBlock(BitsMoE_Qwen3MoeSparseMoeBlock):
 
     def _shared_contribution(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         if hasattr(self, "shared_expert") and hasattr(self, "shared_expert_gate"):
+            y = self._library_dense_mlp(x, self.shared_expert, self.shared_expert_gate)
+            if y is not None:
+                return y
             return torch.sigmoid(self.shared_expert_gate(x)) * self.shared_expert(x)
         return None

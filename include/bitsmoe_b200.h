@@ -204,6 +204,21 @@ BM_API int bm_layer_forward(const bm_layer_t* layer, const void* x, int x_dtype,
                      const int32_t* global_to_local, const void* residual, void* y, int32_t path,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- dense products around the packed experts ---------------------------
+ * Router logits = x @ W_gate^T (the `self.gate(hidden_states)` of bitsmoe/models/qwen3moe/bitsmoe_block.py:45): x [T, hidden]
+ * of x_dtype, gate_w fp16 [num_routed, hidden] -> logits [T, num_routed] of logits_dtype (the reference keeps them in x's type). */
+BM_API int bm_gate_logits(const void* x, int x_dtype, const uint16_t* gate_w, int32_t T, int32_t num_routed, int32_t hidden,
+                          void* logits, int logits_dtype, void* stream);
+/* Dense shared expert(s): y = (silu(x @ Wg^T) * (x @ Wu^T)) @ Wd^T (+ residual), the `shared_experts(identity)` of
+ * bitsmoe/models/deepseekv2/bitsmoe_block.py:123-124; with token_gate_w (fp16 [hidden]) every token's result is scaled by
+ * sigmoid(x . token_gate_w), the gated shared expert of bitsmoe/models/qwen3next/bitsmoe_block.py:144-147.
+ * Weights fp16: w_gate, w_up [intermediate, hidden], w_down [hidden, intermediate].  residual (y_dtype, [T, hidden]) may be
+ * NULL; y may be passed on as the residual of bm_layer_forward / bm_combine_down_basis. */
+BM_API size_t bm_dense_mlp_workspace_bytes(int32_t T, int32_t intermediate);
+BM_API int bm_dense_mlp_forward(const void* x, int x_dtype, const uint16_t* w_gate, const uint16_t* w_up, const uint16_t* w_down,
+                                const uint16_t* token_gate_w, int32_t T, int32_t hidden, int32_t intermediate,
+                                const void* residual, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- expert parallelism ------------------------------------------------
  * The reference has no distributed code (bitsmoe/models/deepseekv2/bitsmoe_block.py:57-62 copies ep_size / ep_rank and
  * never reads them).  These two kernels are the exchange that sharding the experts over the GPUs of one box needs; they

@@ -460,3 +460,44 @@ def test_bounded_wait_gives_up_and_reports_timeout(q30_small):
             packed.check_status()
         packed.check_status()                      # the flag was cleared by the report
     assert float(torch.ones(4, device=DEV).sum()) == 4.0
+
+
+@pytest.mark.parametrize("T,E,H,dtype", [(1, 128, 2048, torch.bfloat16), (64, 128, 2048, torch.bfloat16), (64, 512, 2048, torch.float16),
+                                         (7, 64, 2048, torch.float16), (1000, 128, 2048, torch.bfloat16), (33, 24, 384, torch.float32)])
+def test_gate_logits_vs_fp64(T, E, H, dtype):
+    """Router logits x @ W_gate^T on the library's kernels (cluster split-K for decode sizes, tcgen05 above)."""
+    from bitsmoe_b200.layer import gate_logits
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, H, generator=g).to(dtype)
+    w = (torch.randn(E, H, generator=g) * 0.05).half()
+    want = x.double() @ w.double().T
+    got = gate_logits(x.to(DEV), w.to(DEV))
+    assert got.dtype == dtype and tuple(got.shape) == (T, E)
+    eps = {torch.float32: 2e-3, torch.float16: 2e-3, torch.bfloat16: 8e-3}[dtype]      # one rounding of the output type
+    peak = float(want.abs().max())
+    helpers.assert_close(got, want, rtol=0.0, atol=eps * peak, rel_max=eps, what="gate logits")
+    helpers.assert_detects_damage(got, want, rtol=0.0, atol=eps * peak, rel_max=eps)
+    got32 = gate_logits(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    helpers.assert_close(got32, want, rtol=0.0, atol=2e-3 * peak, rel_max=2e-3, what="gate logits, fp32 out")
+
+
+@pytest.mark.parametrize("T,H,I,gated", [(1, 2048, 512, True), (64, 2048, 512, True), (64, 2048, 2816, False), (9, 256, 160, True),
+                                         (700, 2048, 512, True), (700, 2048, 2816, False)])
+def test_dense_shared_expert_vs_fp64(T, H, I, gated):
+    """Dense shared expert (SwiGLU, optionally sigmoid-gated per token) on the library's kernels against fp64."""
+    from bitsmoe_b200.layer import dense_mlp
+    g = torch.Generator().manual_seed(T + I)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w = {k: (torch.randn(*s, generator=g) * 0.03).half() for k, s in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))}
+    wt = (torch.randn(1, H, generator=g) * 0.05).half() if gated else None
+    want = oforward.dense_mlp(x, w["gate"], w["up"], w["down"]).double()
+    if gated:
+        want = torch.sigmoid(x.double() @ wt.double().T) * want
+    res = torch.randn(T, H, generator=g) * float(want.std())
+    y = dense_mlp(x.to(DEV), w["gate"].to(DEV), w["up"].to(DEV), w["down"].to(DEV), None if wt is None else wt.to(DEV))
+    peak = float(want.abs().max())
+    helpers.assert_close(y, want, rtol=0.0, atol=1.5e-2 * peak, rel_max=1.5e-2, rel_l2=8e-3, what="dense shared expert")
+    helpers.assert_detects_damage(y, want, rtol=0.0, atol=1.5e-2 * peak, rel_max=1.5e-2, rel_l2=8e-3)
+    y2 = dense_mlp(x.to(DEV), w["gate"].to(DEV), w["up"].to(DEV), w["down"].to(DEV), None if wt is None else wt.to(DEV),
+                   residual=res.to(DEV))
+    helpers.assert_close(y2, want + res.to(torch.bfloat16).double(), rtol=0.0, atol=2e-2 * peak, rel_max=2e-2, what="dense shared expert + residual")
