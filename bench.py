@@ -39,7 +39,7 @@ METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 # DRAM bytes (read + write) of one launch of the packed-experts kernel at the decode headline (64 tokens, Qwen3-30B-A3B
 # shape), from a profiler capture; valid only for the arena layout version it was captured with.
-DECODE_KERNEL_DRAM_BYTES = {3: None}
+DECODE_KERNEL_DRAM_BYTES = {3: 25089792}
 
 
 def parse():

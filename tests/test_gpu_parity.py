@@ -180,8 +180,8 @@ def test_experts_forward_q30_shape_vs_oracle_and_reference(q30_small, T):
             outs.append(ref.moe_packed_forward(*args, *ref_lists, layer.cfg.rank, layer.cfg.intermediate, 0).float().clone())
             torch.cuda.synchronize()
         want = torch.stack(outs).median(dim=0).values
-        helpers.assert_close(want, o["rank_accum"], outlier_frac=1e-4, what="reference kernels vs fp32 oracle")
-        helpers.assert_close(got, want, outlier_frac=1e-4, what="rank_accum vs the reference's kernels")
+        helpers.assert_close(want, o["rank_accum"], outlier_frac=1e-3, what="reference kernels vs fp32 oracle")
+        helpers.assert_close(got, want, outlier_frac=1e-3, what="rank_accum vs the reference's kernels")
 
 
 def test_op_shim_matches_reference_contract(q30_small):

@@ -97,13 +97,13 @@ def _check_stage(layer, packed, experts, args, idx, w, path, tag, rtol, atol):
         # calls is the reference value.  Both sides round their operands to fp16 in different places: element-wise the
         # specification's tolerance (rtol 2e-2 / atol 1e-2); what makes the comparison sharp are assert_close's
         # bounds relative to the peak (2e-2) and in L2 (1e-2); even the median keeps single wrong elements at 8192
-        # tokens, so one element in ten thousand may miss the element-wise and peak bounds (never the L2 bound).
+        # tokens, so one element in a thousand may miss the element-wise and peak bounds (never the L2 bound).
         outs = []
         for _ in range(5):
             outs.append(run_ref().float().clone())
             torch.cuda.synchronize()
         ref_out = torch.stack(outs).median(dim=0).values
-        helpers.assert_close(got, ref_out, outlier_frac=1e-4,
+        helpers.assert_close(got, ref_out, outlier_frac=1e-3,
                              what=f"{tag}: fast path vs the reference's kernels (median of five calls)")
 
 
