@@ -59,6 +59,8 @@ _SIGS = {
     "bm_last_error": (C.c_char_p, []),
     "bm_status_string": (C.c_char_p, [C.c_int]),
     "bm_pack_bitplanes_i8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
+    "bm_quantize_pack_slab": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_void_p]),
     "bm_unpack_bitplanes_i8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p]),
     "bm_layer_plan": (C.c_int, [C.POINTER(LayerDesc), C.POINTER(C.c_size_t)]),
     "bm_layer_create": (C.c_int, [C.POINTER(LayerDesc), C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p)]),

@@ -145,8 +145,30 @@ def bucket_segments(segments: Sequence[Tuple[int, Tuple[int, int]]], rank: int) 
     return out
 
 
+def quantize_pack_slab(rows: Tensor, bits: int, want_codes: bool = False):
+    """One slab (<= 64 fp32 rows of one width, on a CUDA device) -> (payload uint32 words in the runtime layout, fp16
+    scales [tiles, k][, int8 codes [k, tiles*128]]) by the library's fused kernel: quantise, bit-plane pack, reorder."""
+    from .. import capi
+    if not rows.is_cuda:
+        raise ValueError("quantize_pack_slab requires CUDA tensors")
+    rows = rows.to(torch.float32)
+    if rows.stride(-1) != 1:
+        rows = rows.contiguous()
+    k, dim = rows.shape
+    tiles = (dim + N_TILE - 1) // N_TILE
+    payload = torch.empty(tiles * k * MICROS_PER_TILE * bits, dtype=torch.int32, device=rows.device)
+    scale = torch.empty((tiles, k), dtype=torch.float16, device=rows.device)
+    codes = torch.empty((k, tiles * N_TILE), dtype=torch.int8, device=rows.device) if want_codes else None
+    with torch.cuda.device(rows.device):
+        capi.check(capi.lib().bm_quantize_pack_slab(rows.data_ptr(), rows.stride(0) if k > 1 else dim, k, dim, bits,
+                                                    payload.data_ptr(), scale.data_ptr(), capi.ptr(codes),
+                                                    capi.stream_ptr(rows.device)))
+    return (payload, scale, codes) if want_codes else (payload, scale)
+
+
 def pack_rank_major(rank_major: Tensor, s_vec: Tensor, segments, groupsize: int = N_TILE,
-                    precomputed: Optional[Dict[int, Tuple[Tensor, Tensor]]] = None) -> Dict[str, Tensor]:
+                    precomputed: Optional[Dict[int, Tuple[Tensor, Tensor]]] = None,
+                    fused: Optional[bool] = None) -> Dict[str, Tensor]:
     """Quantise + pack a rank-major factor [rank, dim].  ``precomputed[bits] = (plane words
     [rank, tiles, 4, bits], scales [rank, tiles])`` lets a caller that quantised and bit-sliced many
     experts in one batch skip both steps.  Buffers stay on the factor's device."""
@@ -160,6 +182,8 @@ def pack_rank_major(rank_major: Tensor, s_vec: Tensor, segments, groupsize: int 
     if dim % N_MICRO:
         raise ValueError(f"dim={dim} must be divisible by microtile width {N_MICRO}")
     dev = rank_major.device
+    if fused is None:
+        fused = dev.type == "cuda" and precomputed is None
     tiles = (dim + N_TILE - 1) // N_TILE
     payload, scales, ridx, s_parts = [], [], [], []
     slab_rows, tile_rows, seg_rows = [], [], []
@@ -182,6 +206,18 @@ def pack_rank_major(rank_major: Tensor, s_vec: Tensor, segments, groupsize: int 
                 padded[:, :dim] = rows[r0:r1].to(torch.float16)
                 words = fp16_to_words(padded).view(k, tiles, MICROS_PER_TILE, 16)
                 sc = torch.ones((k, tiles), dtype=torch.float16, device=dev)
+            elif fused:
+                # quantise + bit-plane pack + reorder in one kernel, straight into the runtime layout
+                pay, sc_t = quantize_pack_slab(rows[r0:r1], bits)
+                payload.append(pay.to(torch.int64) & 0xFFFFFFFF)
+                scales.append(sc_t.reshape(-1))
+                wpt = k * MICROS_PER_TILE * wpr
+                for t in range(tiles):
+                    tile_rows.append([pay_off + t * wpt, sc_off + t * k, min(N_TILE, dim - t * N_TILE)])
+                pay_off += tiles * wpt
+                sc_off += tiles * k
+                ri_off += k
+                continue
             else:
                 if precomputed is not None:
                     w_all, sc_all = precomputed[bits]

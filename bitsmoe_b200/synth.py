@@ -4,8 +4,8 @@ Every routed expert matrix is a rank-major factor ~ N(0, 0.02) with a positive d
 rows get a bit width drawn i.i.d. from the configured distribution and are then ordered so
 that wider rows come first in logical rank order (as an energy-guided allocation would), and
 the result is quantised and packed into exactly the buffers the reference's checkpoints hold
-(bitsmoe/quant/packer.py:711-724).  Quantisation and bit-slicing run batched over all experts
-of a layer on the chosen device; only the per-expert slab assembly is a Python loop.
+(bitsmoe/quant/packer.py:711-724).  On a GPU each slab is quantised, bit-plane packed and reordered by one
+launch of the library's fused kernel; on the host quantisation and bit-slicing run batched over all experts.
 """
 from __future__ import annotations
 
@@ -94,10 +94,14 @@ def make_layer(cfg: LayerConfig, seed: int = 42, device="cpu", keep_full: bool =
         R = normal(E, r, I)
         S = torch.sort(torch.randn(E, r, generator=gen, device=device).abs() + 0.05, dim=1, descending=True).values
         bits = draw_bits(cfg, gen, device)
-        pre = {}
-        for b in sorted({b for b, _ in cfg.bit_probs}):
-            q, sc = packer.quantize_rows(R.view(E * r, I), b)
-            pre[b] = (packer.codes_to_planes(q, b).view(E, r, tiles, packer.MICROS_PER_TILE, b), sc.view(E, r, tiles))
+        # On a GPU every slab goes through the library's fused quantise + pack + reorder kernel; on the host the rows
+        # are quantised and bit-sliced in one batch per width and the slabs assembled from that.
+        pre = None
+        if device.type != "cuda":
+            pre = {}
+            for b in sorted({b for b, _ in cfg.bit_probs}):
+                q, sc = packer.quantize_rows(R.view(E * r, I), b)
+                pre[b] = (packer.codes_to_planes(q, b).view(E, r, tiles, packer.MICROS_PER_TILE, b), sc.view(E, r, tiles))
         bits_cpu = bits.cpu()
         for e in range(E):
             row_bits = bits_cpu[e]
@@ -108,7 +112,8 @@ def make_layer(cfg: LayerConfig, seed: int = 42, device="cpu", keep_full: bool =
                     end += 1
                 segs.append((int(row_bits[start]), (start, end)))
                 start = end
-            buf = packer.pack_rank_major(R[e], S[e], segs, precomputed={b: (pre[b][0][e], pre[b][1][e]) for b in pre})
+            buf = packer.pack_rank_major(R[e], S[e], segs,
+                                         precomputed=None if pre is None else {b: (pre[b][0][e], pre[b][1][e]) for b in pre})
             for f in tables[tag]:
                 tables[tag][f].append(buf[f + "_buffer"])
             if keep_full:

@@ -59,6 +59,15 @@ BM_API const char* bm_status_string(int status);
 BM_API int bm_pack_bitplanes_i8(const int8_t* q, uint32_t* words, int64_t rows, int64_t cols, int bits, void* stream);
 BM_API int bm_unpack_bitplanes_i8(const uint32_t* words, int8_t* q, int64_t rows, int64_t groups, int bits, void* stream);
 
+/* Quantise, bit-plane pack and reorder one slab (<= 64 rank rows of one width) in one kernel: the three steps of
+ * _pack_lowbit_slab_payload_and_scale (bitsmoe/quant/packer.py:210-306) = quantize_symmetric per (row, 128-column tile)
+ * (bitsmoe/quant/quantizer.py:30-84), BitPack.pack, and the [tile][stage][micro][row][plane] reorder (packer.py:169-207).
+ * rows fp32 [k, dim] with row_stride elements between rows; payload uint32 [tiles * k * 4 * bits] and scale fp16
+ * [tiles, k] are the slab's pieces of payload_buffer / scale_buffer; codes (int8 [k, tiles * 128], may be NULL) receives
+ * the signed codes.  bits in {1, 2, 3, 4, 6, 8}. */
+BM_API int bm_quantize_pack_slab(const float* rows, int64_t row_stride, int32_t k, int32_t dim, int32_t bits, uint32_t* payload,
+                                 uint16_t* scale, int8_t* codes, void* stream);
+
 /* ---- layer state -------------------------------------------------------
  * One packed expert matrix exactly as the reference stores it: the six
  * buffers that bitsmoe/models/base_mlp.py:96-102 registers and

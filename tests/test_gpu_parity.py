@@ -501,3 +501,42 @@ def test_dense_shared_expert_vs_fp64(T, H, I, gated):
     y2 = dense_mlp(x.to(DEV), w["gate"].to(DEV), w["up"].to(DEV), w["down"].to(DEV), None if wt is None else wt.to(DEV),
                    residual=res.to(DEV))
     helpers.assert_close(y2, want + res.to(torch.bfloat16).double(), rtol=0.0, atol=2e-2 * peak, rel_max=2e-2, what="dense shared expert + residual")
+
+
+@pytest.mark.parametrize("k_slab,dim,bits", [(13, 160, 4), (64, 256, 2), (38, 384, 3), (5, 96, 8), (16, 128, 1), (9, 224, 6),
+                                             (64, 768, 2), (37, 1408, 3)])
+def test_fused_quantize_pack_slab_matches_oracle_packer(k_slab, dim, bits):
+    """One kernel = quantize_symmetric per (row, tile) + bit-plane pack + stage/micro reorder: its payload words and
+    scales must be what the oracle packer (pinned to the reference's own packer by the golden fixtures) produces."""
+    import os
+    from bitsmoe_b200.quant import packer as ppacker
+    G = np.load(os.path.join(os.path.dirname(__file__), "golden", "format_golden.npz"))
+    key = f"slab_x_k{k_slab}_d{dim}_b{bits}"
+    x = torch.from_numpy(G[key]) if key in G else torch.randn(k_slab, dim, generator=torch.Generator().manual_seed(k_slab + dim)) * 0.02
+    want = opacker.pack_matrix(x, torch.ones(k_slab), [(bits, (0, k_slab))])
+    pay, sc, codes = ppacker.quantize_pack_slab(x.to(DEV), bits, want_codes=True)
+    got_pay = (pay.cpu().to(torch.int64) & 0xFFFFFFFF).numpy().astype(np.uint32)
+    assert np.array_equal(got_pay, np.asarray(want["payload_buffer"]).reshape(-1)), "payload words"
+    assert np.array_equal(sc.cpu().numpy().reshape(-1).view(np.uint16), np.asarray(want["scale_buffer"]).reshape(-1).view(np.uint16)), "scales"
+    dec = opacker.decode_matrix(want, dim)
+    assert np.array_equal(codes.cpu().numpy()[:, :dim], dec["codes"][:, :dim])
+    if key in G:     # and the reference's own packer output for the same slab
+        assert np.array_equal(got_pay, G[f"slab_payload_k{k_slab}_d{dim}_b{bits}"].reshape(-1))
+        assert np.array_equal(sc.cpu().numpy().reshape(-1).view(np.uint16), G[f"slab_scale_k{k_slab}_d{dim}_b{bits}"].reshape(-1).view(np.uint16))
+
+
+def test_fused_packer_path_builds_the_same_layer_as_the_host_path():
+    """synth.make_layer on the GPU (fused kernel per slab) and on the host (batched torch ops): same buffers."""
+    cfg = synth.LayerConfig("fused-pack", 256, 6, 384, 2, rank=80, bit_probs=((1, 0.1), (2, 0.5), (3, 0.25), (4, 0.15)))
+    from bitsmoe_b200.quant import packer as ppacker
+    g = torch.Generator().manual_seed(5)
+    R = torch.randn(80, 384, generator=g) * 0.02
+    S = torch.rand(80, generator=g) + 0.2
+    segs = [(4, (0, 9)), (3, (9, 30)), (2, (30, 70)), (1, (70, 76)), (0, (76, 80))]
+    host = ppacker.pack_rank_major(R, S, segs)
+    dev = ppacker.pack_rank_major(R.to(DEV), S.to(DEV), segs)
+    for key in ("payload_buffer", "scale_buffer", "rank_idx_buffer", "tile_meta_buffer", "slab_meta_buffer", "s_buffer"):
+        a, b = host[key], dev[key].cpu()
+        if a.dtype == torch.uint32:
+            a, b = a.to(torch.int64), b.to(torch.int64)
+        assert torch.equal(a, b), key
