@@ -12,6 +12,10 @@ Two workloads, both "one step = one forward of one packed MoE layer over one bat
           expert-parallel over the N GPUs (strong scaling: the batch is split over the ranks, experts are sharded,
           rank-space rows are exchanged through peer memory).  N = 1 is the same layer and batch on one GPU.
 
+  stack   (explicit only) 48 Qwen3-30B-A3B-shaped decoder layers: bf16 torch attention (32 query / 4 KV heads of 128, 2048
+          tokens in the KV cache) and RMSNorm around this library's MoE block (router Linear included), one decode step of
+          64 sequences, expert-parallel over the N GPUs; end-to-end tokens/s.
+
 --workload auto (the default) picks `ep` when the process is one of several ranks or when several GPUs are visible
 (the run is then one point of a 1/2/4/8-GPU series, which has to be one workload), else `decode`.
 Rank 0 prints one JSON line.  `--impl reference` times the CPU dequantise-then-matmul path of the same workload on
@@ -48,7 +52,10 @@ def parse():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto", "decode", "ep"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "decode", "ep", "stack"])
+    ap.add_argument("--stack-layers", type=int, default=48, help="stack workload: decoder layers")
+    ap.add_argument("--stack-batch", type=int, default=64, help="stack workload: sequences decoded per step, over all GPUs")
+    ap.add_argument("--stack-context", type=int, default=2048, help="stack workload: tokens already in the KV cache")
     ap.add_argument("--tokens", type=int, default=64, help="decode batch of the headline number")
     ap.add_argument("--layers", type=int, default=12, help="distinct weight sets rotated through (decode workload)")
     ap.add_argument("--prefill-tokens", type=int, default=8192)
@@ -506,6 +513,22 @@ def decode_arm(args):
                              "kernel_ms": kms, "algorithmic_flops": flops_experts}}
         except Exception as ex:  # keep the headline if the large case fails
             extra["prefill_error"] = repr(ex)
+        # the same step with the router Linear inside it (x @ W_gate^T by the library instead of ready-made logits)
+        try:
+            from bitsmoe_b200.layer import gate_logits
+            T = args.tokens
+            gw = [(torch.randn(cfg.num_experts, cfg.hidden, device=dev) * 0.02).half() for _ in range(L)]
+            xs = [synth.activations(cfg, T, seed=7 + i, device=dev) for i in range(L)]
+            ys = [torch.empty_like(xs[0]) for _ in range(L)]
+            gstep = lambda i: layers[i % L].forward(xs[i % L], gate_logits(xs[i % L], gw[i % L]), cfg.top_k, True, torch.bfloat16,
+                                                    out=ys[i % L], path=args.path)
+            for i in range(3):
+                gstep(i)
+            gms = timed(gstep, args.steps, sync) / args.steps
+            extra[f"decode_{T}_with_router_linear"] = {"tokens": T, "ms_per_step": gms, "tokens_per_s": T / (gms * 1e-3),
+                                                       "note": "router logits computed inside the step (bm_gate_logits), then the same five launches"}
+        except Exception as ex:
+            extra["router_linear_error"] = repr(ex)
         # the kernels to beat: the reference's own CUDA op, recompiled for sm_100a, at the op boundary on the same inputs
         try:
             ref = load_reference_kernels()
@@ -717,6 +740,97 @@ def ep_arm(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------- stack workload
+def stack_arm(args):
+    """One decode step of a 48-layer stack (BASELINE.json configs[4]): per layer RMSNorm -> attention over a 2048-token
+    KV cache (bf16 torch: library GEMMs and scaled_dot_product_attention) -> RMSNorm -> this library's MoE block
+    (router Linear, routing, packed experts, down basis), expert-parallel over the ranks.  Weights are seeded random."""
+    from bitsmoe_b200 import capi, ep, synth
+    from bitsmoe_b200.layer import PackedLayer, gate_logits
+    import torch.nn.functional as F
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    init_dist(dev, world)
+    cfg = synth.QWEN3_30B
+    NL, B, CTX = args.stack_layers, args.stack_batch, args.stack_context
+    if B % world:
+        raise SystemExit(f"--stack-batch {B} must be a multiple of the number of GPUs")
+    Bl = B // world
+    H, NH, NKV, HD = cfg.hidden, 32, 4, 128
+    sync = lambda: torch.cuda.synchronize(dev)
+    g = torch.Generator(device=dev).manual_seed(1234)          # replicated weights: the same seed on every rank
+    rnd = lambda *shape, std=0.02: (torch.randn(*shape, generator=g, device=dev) * std).to(torch.bfloat16)
+    layers = []
+    t_build = time.perf_counter()
+    for li in range(NL):
+        s = synth.make_layer(cfg, seed=42 + li, device=dev)
+        if world > 1:
+            t = ep.shard_tables(s.tables, rank, world)
+            pk = PackedLayer(t["gate"], t["up"], t["down"], cfg.intermediate, cfg.rank, s.vh_gate, s.vh_up, s.u_down, device=dev)
+            moe = ep.SymmetricExpertParallel(pk, cfg.num_experts, cfg.top_k, Bl, cfg.norm_topk_prob)
+        else:
+            pk = synth.to_packed_layer(s, dev)
+            moe = None
+        layers.append(dict(
+            pk=pk, moe=moe, wq=rnd(NH * HD, H), wk=rnd(NKV * HD, H), wv=rnd(NKV * HD, H), wo=rnd(H, NH * HD),
+            gate=rnd(cfg.num_experts, H).half(), n1=torch.ones(H, device=dev, dtype=torch.bfloat16),
+            n2=torch.ones(H, device=dev, dtype=torch.bfloat16),
+            kc=rnd(Bl, NKV, CTX + 1, HD, std=1.0), vc=rnd(Bl, NKV, CTX + 1, HD, std=1.0)))
+        del s
+    t_build = time.perf_counter() - t_build
+    x0 = torch.randn(Bl, H, generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(x0)
+
+    def step(_i=0):
+        x = x0
+        for ly in layers:
+            h = F.rms_norm(x, (H,), ly["n1"], 1e-6)
+            q = (h @ ly["wq"].T).view(Bl, NH, 1, HD)
+            ly["kc"][:, :, CTX] = (h @ ly["wk"].T).view(Bl, NKV, HD)
+            ly["vc"][:, :, CTX] = (h @ ly["wv"].T).view(Bl, NKV, HD)
+            a = F.scaled_dot_product_attention(q, ly["kc"], ly["vc"], enable_gqa=True)
+            x = x + a.reshape(Bl, NH * HD) @ ly["wo"].T
+            h = F.rms_norm(x, (H,), ly["n2"], 1e-6)
+            logits = gate_logits(h, ly["gate"])
+            if ly["moe"] is None:
+                x = ly["pk"].forward(h, logits, cfg.top_k, cfg.norm_topk_prob, torch.bfloat16, residual=x)
+            else:
+                x = ly["moe"].forward(h, logits, torch.bfloat16, residual=x, overlap=False)
+        out.copy_(x)
+
+    for _ in range(3):
+        step()
+    sync()
+    if world > 1:
+        torch.distributed.barrier()
+    steps = max(1, min(args.steps, 50))
+    with ClockSampler(local) as clk:
+        n0 = int(capi.lib().bm_launch_count())
+        ms = timed(step, steps, sync, use_graph=True) / steps
+        launches = int(capi.lib().bm_launch_count()) - n0
+    clocks = clk.summary()
+    for ly in layers:
+        ly["pk"].check_status()
+    finite = bool(torch.isfinite(out.float()).all())
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t[0])
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+    if rank != 0:
+        return
+    print(json.dumps({
+        "metric": "stack_decode_tokens_per_s", "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": 3,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 attention, f16 experts",
+        "data": "synthetic",
+        "config": {"workload": f"{NL} qwen3-30b-a3b-shaped decoder layers, one decode step of {B} sequences, {CTX}-token KV cache, "
+                               f"expert-parallel over {world} GPU(s)", "batch_per_gpu": Bl,
+                   "launch": "the whole step captured in one CUDA graph per rank", "attention": "torch bf16 (library kernels)"},
+        "gpu_launches": launches, "clocks": clocks, "extra": {"output_finite": finite, "layer_build_s": t_build}}), flush=True)
+
+
 if __name__ == "__main__":
     a = parse()
     _, _world, _ = dist_env()
@@ -724,6 +838,8 @@ if __name__ == "__main__":
         reference_arm(a)
     elif a.probe:
         probe(a)
+    elif pick_workload(a, _world) == "stack":
+        stack_arm(a)
     elif pick_workload(a, _world) == "ep":
         ep_arm(a)
     else:

@@ -135,6 +135,15 @@ __device__ __forceinline__ void store_act(void* p, int dtype, int64_t i, float v
   else reinterpret_cast<float*>(p)[i] = v;
 }
 
+// Accumulation into rank_accum: fp32 atomics (as bitsmoe/algorithms/cpp/mlp_forward.cu:2062 does), or -- the
+// deterministic mode -- 64-bit fixed-point atomics: integer addition is associative, so the sum does not depend on the
+// order in which CTAs arrive and two runs are bit-identical.  2^40 leaves 2^23 of range and 1e-12 of resolution.
+constexpr float ACC_FIXED_SCALE = 1099511627776.f;
+__device__ __forceinline__ void acc_add(float* __restrict__ acc32, long long* __restrict__ acc64, int64_t idx, float v) {
+  if (acc64) atomicAdd(reinterpret_cast<unsigned long long*>(acc64) + idx, static_cast<unsigned long long>(__float2ll_rn(v * ACC_FIXED_SCALE)));
+  else atomicAdd(acc32 + idx, v);
+}
+
 // C[M,N] = A[M,K] . B[N,K]^T ; up to two problems sharing A's shape in one launch.
 struct GemmArgs {
   const void* A[2];
@@ -169,6 +178,7 @@ struct bm_layer {
   int max_unit_bytes = 0, max_slots = 0, max_words = 0;
   // launch geometry of the decode kernel on this layer's device (plan_experts_decode)
   bool dec_ok = false;
+  bool deterministic = false;      // rank_accum through 64-bit fixed-point atomics (bm_layer_set_option)
   int dec_ring = 0, dec_sec_bytes = 0, dec_grid = 0, dec_act_bufs = 2, dec_ctas = 0, dec_force_ctas = 0;
   size_t dec_smem = 0;
   int* status_dev = nullptr;       // device flag set by a kernel whose bounded wait gave up

@@ -74,6 +74,7 @@ struct DecParams {
   const int32_t* expert_offsets;
   const float* route_w;
   float* rank_accum;
+  long long* acc64;      // deterministic mode: 64-bit fixed-point accumulators instead of rank_accum (else null)
   int* status;
   int h_rank, rank_out, T, num_experts, n_tiles, intermediate;
   int max_slots, sec_bytes, ring;
@@ -628,7 +629,7 @@ __global__ void __launch_bounds__(DEC_THREADS) experts_decode_kernel(const DecPa
             for (int h = 0; h < 2; ++h) {
               const int n = 2 * t + h;
               if (n >= npass) continue;
-              atomicAdd(&P.rank_accum[static_cast<int64_t>(si.tok[n]) * P.rank_out + rk], dtot[i2][2 * hr + h] * sv * si.rw[n]);
+              acc_add(P.rank_accum, P.acc64, static_cast<int64_t>(si.tok[n]) * P.rank_out + rk, dtot[i2][2 * hr + h] * sv * si.rw[n]);
             }
           }
         }
@@ -699,7 +700,7 @@ bool experts_decode_fits(const bm_layer* L) { return L->dec_ok; }
 
 int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                           const int32_t* expert_offsets, const float* route_w, int T, int num_assign, float* rank_accum,
-                          cudaStream_t st) {
+                          long long* acc64, cudaStream_t st) {
   BM_REQUIRE(num_assign / FAST_MAX_TOK + L->num_experts < 60000, BM_ERR_UNSUPPORTED,
              "experts_decode: %d assignments are too many passes for the decode path", num_assign);
   BM_REQUIRE(L->dec_ok, BM_ERR_UNSUPPORTED, "experts_decode: a unit of %d slots / %d words does not fit shared memory",
@@ -715,6 +716,7 @@ int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half*
   P.expert_offsets = expert_offsets;
   P.route_w = route_w;
   P.rank_accum = rank_accum;
+  P.acc64 = acc64;
   P.status = L->status_dev;
   P.h_rank = L->rank_in;
   P.rank_out = L->rank_out;

@@ -84,7 +84,7 @@ __device__ __forceinline__ void down_row(const uint32_t* __restrict__ tile_paylo
 __global__ void __launch_bounds__(GEN_THREADS) experts_generic_kernel(
     const ExpertDev* __restrict__ experts, const __half* __restrict__ h_gate, const __half* __restrict__ h_up, int h_rank,
     const int32_t* __restrict__ token_indices, const int32_t* __restrict__ expert_offsets,
-    const float* __restrict__ route_w, int rank_out, int max_rows, int T, float* __restrict__ rank_accum) {
+    const float* __restrict__ route_w, int rank_out, int max_rows, int T, float* __restrict__ rank_accum, long long* __restrict__ acc64) {
   extern __shared__ float sm[];
   float* hs = sm;                               // [2][GEN_NA][max_rows]
   float* z = sm + 2 * GEN_NA * max_rows;        // [GEN_NA][N_TILE]
@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(GEN_THREADS) experts_generic_kernel(
       for (int a = 0; a < GEN_NA; ++a) {
         if (a < na) {
           const float v = acc[a] * f * rw[a];
-          if (v != 0.f) atomicAdd(&rank_accum[static_cast<int64_t>(tok[a]) * rank_out + logical], v);
+          if (v != 0.f) acc_add(rank_accum, acc64, static_cast<int64_t>(tok[a]) * rank_out + logical, v);
         }
       }
     }
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(GEN_THREADS) experts_generic_kernel(
 
 int launch_experts_generic(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                            const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum,
-                           cudaStream_t st) {
+                           long long* acc64, cudaStream_t st) {
   const size_t smem = sizeof(float) * (2 * GEN_NA * L->max_rows + GEN_NA * N_TILE);
   BM_REQUIRE(smem <= 200 * 1024, BM_ERR_UNSUPPORTED, "experts_generic: %d stored rows per matrix exceed shared memory",
              L->max_rows);
@@ -208,7 +208,7 @@ int launch_experts_generic(const bm_layer* L, const __half* h_gate, const __half
   dim3 grid(L->n_tiles, L->num_experts);
   experts_generic_kernel<<<grid, GEN_THREADS, smem, st>>>(L->experts_dev, h_gate, h_up, L->rank_in, token_indices,
                                                          expert_offsets, route_w, L->rank_out, L->max_rows, T,
-                                                         rank_accum);
+                                                         rank_accum, acc64);
   BM_LAUNCH_CHECK("experts_generic_kernel");
   return BM_OK;
 }

@@ -130,7 +130,8 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
     const FastExpert* __restrict__ fast, const unsigned char* __restrict__ arena, const __half* __restrict__ h_gate,
     const __half* __restrict__ h_up, int h_rank, const int32_t* __restrict__ token_indices,
     const int32_t* __restrict__ expert_offsets, const float* __restrict__ route_w, int rank_out, int T, int num_experts,
-    int n_tiles, int max_slots, int max_words, float* __restrict__ rank_accum, int* __restrict__ status) {
+    int n_tiles, int max_slots, int max_words, float* __restrict__ rank_accum, long long* __restrict__ acc64,
+    int* __restrict__ status) {
   extern __shared__ unsigned char xt_raw[];
   __shared__ __align__(8) XtBars bars;
   __shared__ XtItem item;
@@ -496,7 +497,7 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 const int n = n0 + i;
-                if (n < n_tok) atomicAdd(&rank_accum[static_cast<int64_t>(item.tok[n]) * rank_out + rk], v[i] * sv * item.rw[n]);
+                if (n < n_tok) acc_add(rank_accum, acc64, static_cast<int64_t>(item.tok[n]) * rank_out + rk, v[i] * sv * item.rw[n]);
               }
             }
           }
@@ -525,7 +526,8 @@ bool experts_tc_fits(const bm_layer* L) {
 }
 
 int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
-                      const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st) {
+                      const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, long long* acc64,
+                      cudaStream_t st) {
   BM_REQUIRE(L->num_experts <= XT_MAX_E, BM_ERR_UNSUPPORTED, "experts_tc: more than %d experts", XT_MAX_E);
   BM_REQUIRE(L->intermediate % N_TILE == 0, BM_ERR_UNSUPPORTED, "experts_tc: intermediate size must be a multiple of %d", N_TILE);
   BM_REQUIRE(L->max_slots <= 3 * 128, BM_ERR_UNSUPPORTED, "experts_tc: %d row slots exceed the tensor-memory budget", L->max_slots);
@@ -540,7 +542,7 @@ int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_u
   }
   experts_tc_kernel<<<sm_count, XT_THREADS, smem, st>>>(
       L->fast_dev, static_cast<const unsigned char*>(L->arena), h_gate, h_up, L->rank_in, token_indices, expert_offsets,
-      route_w, L->rank_out, T, L->num_experts, L->n_tiles, L->max_slots, L->max_words, rank_accum, L->status_dev);
+      route_w, L->rank_out, T, L->num_experts, L->n_tiles, L->max_slots, L->max_words, rank_accum, acc64, L->status_dev);
   BM_LAUNCH_CHECK("experts_tc_kernel");
   return BM_OK;
 }

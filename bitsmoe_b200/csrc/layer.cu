@@ -57,13 +57,14 @@ int launch_arena_decode(const bm_layer* L, int e, int w, int8_t* codes, cudaStre
 int plan_experts_decode(bm_layer* L);
 int launch_experts_decode(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                           const int32_t* expert_offsets, const float* route_w, int T, int num_assign, float* rank_accum,
-                          cudaStream_t st);
+                          long long* acc64, cudaStream_t st);
 bool experts_tc_fits(const bm_layer* L);
 int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
-                      const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, cudaStream_t st);
+                      const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum, long long* acc64,
+                      cudaStream_t st);
 int launch_experts_generic(const bm_layer* L, const __half* h_gate, const __half* h_up, const int32_t* token_indices,
                            const int32_t* expert_offsets, const float* route_w, int T, float* rank_accum,
-                           cudaStream_t st);
+                           long long* acc64, cudaStream_t st);
 
 static const char* which_name(int w) { return w == 0 ? "gate" : (w == 1 ? "up" : "down"); }
 
@@ -361,6 +362,11 @@ extern "C" int64_t bm_layer_expert_bytes(const bm_layer_t* L, int32_t e) {
 
 extern "C" int bm_layer_set_option(bm_layer_t* L, int32_t option, int32_t value) {
   BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "set_option: null layer");
+  if (option == BM_OPT_DETERMINISTIC) {
+    BM_REQUIRE(value == 0 || value == 1, BM_ERR_INVALID_ARG, "set_option: the deterministic mode is 0 or 1");
+    L->deterministic = value != 0;
+    return BM_OK;
+  }
   BM_REQUIRE(option == BM_OPT_DECODE_CTAS_PER_SM, BM_ERR_INVALID_ARG, "set_option: unknown option %d", option);
   BM_REQUIRE(value >= 0 && value <= 3, BM_ERR_INVALID_ARG, "set_option: CTAs per SM must be 0..3");
   const bm_layer saved = *L;
@@ -459,46 +465,76 @@ extern "C" int bm_basis_project(const bm_layer_t* L, const void* x, int x_dtype,
   return basis_project_impl(L, x, x_dtype, T, h_gate, h_up, nullptr, 0, nullptr, stream);
 }
 
+// fixed-point accumulators -> fp32 rank_accum (deterministic mode)
+__global__ void __launch_bounds__(256) acc64_to_f32_kernel(const long long* __restrict__ acc64, float* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    out[i] = static_cast<float>(static_cast<double>(acc64[i]) * (1.0 / static_cast<double>(ACC_FIXED_SCALE)));
+}
+
+static size_t experts_ws_need(const bm_layer_t* L, int32_t T) {
+  return (L && L->deterministic) ? align_up(sizeof(long long) * static_cast<size_t>(T) * L->rank_out, 256) : 0;
+}
+
 extern "C" size_t bm_experts_workspace_bytes(const bm_layer_t* L, int32_t T, int32_t num_assign, int32_t path) {
-  (void)L; (void)T; (void)num_assign; (void)path;
-  return 0;
+  (void)num_assign; (void)path;
+  return T > 0 ? experts_ws_need(L, T) : 0;
 }
 
 static int experts_forward_impl(const bm_layer_t* L, const uint16_t* h_gate, const uint16_t* h_up,
                                 const int32_t* token_indices, const int32_t* expert_offsets, const float* route_weights,
                                 int32_t T, int32_t num_assign, float* rank_accum, int32_t path, bool already_zero,
-                                void* stream) {
+                                void* workspace, size_t workspace_bytes, void* stream) {
   BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "experts_forward: null layer");
   BM_REQUIRE(T >= 0 && num_assign >= 0, BM_ERR_INVALID_ARG, "experts_forward: negative sizes");
   BM_REQUIRE(path >= BM_PATH_AUTO && path <= BM_PATH_TENSOR, BM_ERR_INVALID_ARG, "experts_forward: unknown path %d", path);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (T == 0) return BM_OK;
   BM_REQUIRE(rank_accum, BM_ERR_INVALID_ARG, "experts_forward: null rank_accum");
-  if (!already_zero) BM_CUDA(cudaMemsetAsync(rank_accum, 0, sizeof(float) * static_cast<size_t>(T) * L->rank_out, st));
-  if (num_assign == 0 || L->num_experts == 0) return BM_OK;
+  long long* acc64 = nullptr;
+  const int64_t n_acc = static_cast<int64_t>(T) * L->rank_out;
+  if (L->deterministic) {
+    const size_t need = experts_ws_need(L, T);
+    BM_REQUIRE(workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0, BM_ERR_WORKSPACE,
+               "experts_forward: the deterministic mode needs a 16-byte aligned workspace of %zu bytes (%zu given)", need, workspace_bytes);
+    acc64 = static_cast<long long*>(workspace);
+    BM_CUDA(cudaMemsetAsync(acc64, 0, sizeof(long long) * static_cast<size_t>(n_acc), st));
+  } else if (!already_zero) {
+    BM_CUDA(cudaMemsetAsync(rank_accum, 0, sizeof(float) * static_cast<size_t>(n_acc), st));
+  }
+  int rc = BM_OK;
+  if (num_assign == 0 || L->num_experts == 0) {
+    if (acc64) BM_CUDA(cudaMemsetAsync(rank_accum, 0, sizeof(float) * static_cast<size_t>(n_acc), st));
+    return BM_OK;
+  }
   BM_REQUIRE(h_gate && h_up && token_indices && expert_offsets && route_weights, BM_ERR_INVALID_ARG,
              "experts_forward: null pointer");
   BM_REQUIRE(path != BM_PATH_TENSOR || L->fast_ok, BM_ERR_UNSUPPORTED,
              "experts_forward: the tensor path needs 1- to 4-bit rows and full tiles; this layer has neither");
-  if (L->fast_ok && (path == BM_PATH_TENSOR || (path == BM_PATH_AUTO && num_assign > 16 * L->num_experts && experts_tc_fits(L))))
-    return launch_experts_tc(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up), token_indices,
-                             expert_offsets, route_weights, T, rank_accum, st);
   BM_REQUIRE(path != BM_PATH_DECODE || L->fast_ok, BM_ERR_UNSUPPORTED,
              "experts_forward: the decode path needs 1- to 4-bit rows and full tiles; this layer has neither");
-  if (L->fast_ok && (path == BM_PATH_DECODE || (path != BM_PATH_GENERIC && L->dec_ok && num_assign / 8 + L->num_experts < 60000)))
-    return launch_experts_decode(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
-                                 token_indices, expert_offsets, route_weights, T, num_assign, rank_accum, st);
-  return launch_experts_generic(L, reinterpret_cast<const __half*>(h_gate), reinterpret_cast<const __half*>(h_up),
-                                token_indices, expert_offsets, route_weights, T, rank_accum, st);
+  const __half* hg = reinterpret_cast<const __half*>(h_gate);
+  const __half* hu = reinterpret_cast<const __half*>(h_up);
+  if (L->fast_ok && (path == BM_PATH_TENSOR || (path == BM_PATH_AUTO && num_assign > 16 * L->num_experts && experts_tc_fits(L))))
+    rc = launch_experts_tc(L, hg, hu, token_indices, expert_offsets, route_weights, T, rank_accum, acc64, st);
+  else if (L->fast_ok && (path == BM_PATH_DECODE || (path != BM_PATH_GENERIC && L->dec_ok && num_assign / 8 + L->num_experts < 60000)))
+    rc = launch_experts_decode(L, hg, hu, token_indices, expert_offsets, route_weights, T, num_assign, rank_accum, acc64, st);
+  else
+    rc = launch_experts_generic(L, hg, hu, token_indices, expert_offsets, route_weights, T, rank_accum, acc64, st);
+  if (rc) return rc;
+  if (acc64) {
+    const int blocks = static_cast<int>((n_acc + 255) / 256 < 148 * 8 ? (n_acc + 255) / 256 : 148 * 8);
+    acc64_to_f32_kernel<<<blocks, 256, 0, st>>>(acc64, rank_accum, n_acc);
+    BM_LAUNCH_CHECK("acc64_to_f32_kernel");
+  }
+  return BM_OK;
 }
 
 extern "C" int bm_experts_forward(const bm_layer_t* L, const uint16_t* h_gate, const uint16_t* h_up,
                                   const int32_t* token_indices, const int32_t* expert_offsets,
                                   const float* route_weights, int32_t T, int32_t num_assign, float* rank_accum,
                                   int32_t path, void* workspace, size_t workspace_bytes, void* stream) {
-  (void)workspace; (void)workspace_bytes;
   return experts_forward_impl(L, h_gate, h_up, token_indices, expert_offsets, route_weights, T, num_assign, rank_accum, path,
-                              false, stream);
+                              false, workspace, workspace_bytes, stream);
 }
 
 extern "C" int bm_combine_down_basis(const bm_layer_t* L, const float* rank_accum, int32_t T, const void* residual,
@@ -586,7 +622,8 @@ extern "C" int bm_layer_forward(const bm_layer_t* L, const void* x, int x_dtype,
   // Dropped assignments (experts that are not packed) leave a shorter list; the kernels walk
   // expert_offsets, so passing the upper bound T*k as num_assign is safe.
   rc = experts_forward_impl(L, reinterpret_cast<const uint16_t*>(w.h_gate), reinterpret_cast<const uint16_t*>(w.h_up),
-                            w.token_indices, w.expert_offsets, w.route_flat, T, T * k, w.rank_accum, path, zeroed, stream);
+                            w.token_indices, w.expert_offsets, w.route_flat, T, T * k, w.rank_accum, path, zeroed, w.experts_ws,
+                            w.experts_ws_bytes, stream);
   if (rc) return rc;
   return bm_combine_down_basis(L, w.rank_accum, T, residual, y, x_dtype == BM_F32 ? BM_F32 : x_dtype, stream);
 }

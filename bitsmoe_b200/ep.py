@@ -388,9 +388,12 @@ class SymmetricExpertParallel:
             capi.check(lib.bm_route_build(rt[0].data_ptr(), rt[1].data_ptr(), self.g2l.data_ptr(), self.g2l.numel(), G * T, k,
                                           self.per, 128, sc["tok"].data_ptr(), sc["off"].data_ptr(), sc["rw"].data_ptr(), None,
                                           None, sc["ws"].data_ptr(), sc["ws"].numel(), st))
+            need = int(lib.bm_experts_workspace_bytes(pk._handle, G * T, G * T * k, capi.PATH_AUTO))
+            if need and (sc.get("xws") is None or sc["xws"].numel() < need):
+                sc["xws"] = torch.empty(need, dtype=torch.uint8, device=pk.device)      # deterministic mode only
             capi.check(lib.bm_experts_forward(pk._handle, h[0].data_ptr(), h[1].data_ptr(), sc["tok"].data_ptr(),
                                               sc["off"].data_ptr(), sc["rw"].data_ptr(), G * T, G * T * k, part.data_ptr(),
-                                              capi.PATH_AUTO, None, 0, st))
+                                              capi.PATH_AUTO, capi.ptr(sc.get("xws")) if need else None, need, st))
             capi.check(lib.bm_ep_barrier(pk._handle, self._flags, G, self.rank, 2 * area + 1, self.barrier_limit_ms, st))
             capi.check(lib.bm_ep_pull_reduce(p_tab, idx_mine.data_ptr(), G, self.rank, T, r_out, k, self.per,
                                              sc["acc"].data_ptr(), st))

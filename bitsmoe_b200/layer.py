@@ -128,6 +128,15 @@ class PackedLayer:
     def has_fast_layout(self) -> bool:
         return bool(capi.lib().bm_layer_has_fast_layout(self._handle))
 
+    def set_deterministic(self, on: bool = True) -> None:
+        """Packed-expert kernels add into rank_accum through 64-bit fixed-point atomics: bit-identical results from run
+        to run (the reference's fp32 atomics, bitsmoe/algorithms/cpp/mlp_forward.cu:2062, depend on arrival order)."""
+        capi.check(capi.lib().bm_layer_set_option(self._handle, 1, int(bool(on))))
+        self._ws.clear()
+
+    def set_decode_ctas_per_sm(self, n: int = 0) -> None:
+        capi.check(capi.lib().bm_layer_set_option(self._handle, 0, int(n)))
+
     def check_status(self) -> None:
         """Synchronises and raises if a kernel of this layer gave up a bounded device-side wait."""
         with torch.cuda.device(self.device):

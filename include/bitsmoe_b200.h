@@ -126,8 +126,12 @@ BM_API int bm_layer_status(const bm_layer_t* layer, void* stream);
 
 /* No counterpart in the reference.  Tuning knobs of a layer; set between forwards, never while one is in flight.
  *   BM_OPT_DECODE_CTAS_PER_SM: resident CTAs per SM of the decode kernel (1, 2 or 3; 0 = the library's choice).
+ *   BM_OPT_DETERMINISTIC (0 / 1): the packed-expert kernels add into rank_accum through 64-bit fixed-point atomics
+ *     instead of fp32 atomics (bitsmoe/algorithms/cpp/mlp_forward.cu:2062 uses fp32 atomics, whose result depends on
+ *     arrival order): two runs on the same inputs are then bit-identical.  bm_experts_workspace_bytes /
+ *     bm_layer_workspace_bytes grow by 8 bytes per rank_accum element; ask them again after switching.
  * Returns BM_ERR_UNSUPPORTED when the layer's working set does not fit the requested geometry (nothing changes). */
-enum { BM_OPT_DECODE_CTAS_PER_SM = 0 };
+enum { BM_OPT_DECODE_CTAS_PER_SM = 0, BM_OPT_DETERMINISTIC = 1 };
 BM_API int bm_layer_set_option(bm_layer_t* layer, int32_t option, int32_t value);
 
 /* No counterpart in the reference.  Launches a one-warp kernel whose only job is to wait (at most limit_us
@@ -191,6 +195,7 @@ BM_API int bm_route(const void* logits, int logits_dtype, int32_t T, int32_t E_r
  * (bitsmoe/models/qwen3moe/bitsmoe_block.py:63-64).  x [T, hidden] of x_dtype. */
 BM_API int bm_basis_project(const bm_layer_t* layer, const void* x, int x_dtype, int32_t T,
                      uint16_t* h_gate, uint16_t* h_up, void* stream);
+/* Scratch bm_experts_forward needs: 0, or the fixed-point accumulators of the deterministic mode. */
 BM_API size_t bm_experts_workspace_bytes(const bm_layer_t* layer, int32_t T, int32_t num_assign, int32_t path);
 /* The op contract of moe_packed_forward (bitsmoe/algorithms/cpp/mlp_forward_binding.cpp:53-155,
  * bitsmoe/algorithms/cpp/mlp_forward.cu:2701-3074): rank_accum fp32 [T, rank_out] is

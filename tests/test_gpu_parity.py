@@ -540,3 +540,28 @@ def test_fused_packer_path_builds_the_same_layer_as_the_host_path():
         if a.dtype == torch.uint32:
             a, b = a.to(torch.int64), b.to(torch.int64)
         assert torch.equal(a, b), key
+
+
+@pytest.mark.parametrize("path,T", [(capi.PATH_DECODE, 64), (capi.PATH_TENSOR, 700), (capi.PATH_GENERIC, 40)])
+def test_deterministic_mode_is_bit_reproducible(q30_small, path, T):
+    """With fixed-point accumulation two runs give identical bits whatever order the CTAs arrive in, and the values
+    agree with the fp32-atomic mode to fp32 rounding."""
+    layer, packed, experts = q30_small
+    x, logits = _inputs(layer, T, 900 + T)
+    logits = synth.router_logits(layer.cfg, T, seed=901 + T, zipf_s=1.5)          # several experts get many tokens: many adds per element
+    o = oforward.layer_forward(x, logits, layer.vh_gate.cpu(), layer.vh_up.cpu(), layer.u_down.cpu(), experts, layer.cfg.top_k)
+    args = [o[k].to(DEV) for k in ("h_gate", "h_up", "token_indices", "expert_offsets", "route_flat")]
+    plain = packed.experts_forward(*args, path=path)
+    packed.set_deterministic(True)
+    try:
+        runs = [packed.experts_forward(*args, path=path).clone() for _ in range(4)]
+        y1 = packed.forward(x.to(DEV), logits.to(DEV), layer.cfg.top_k, True, torch.bfloat16, path=path).clone()
+        y2 = packed.forward(x.to(DEV), logits.to(DEV), layer.cfg.top_k, True, torch.bfloat16, path=path).clone()
+    finally:
+        packed.set_deterministic(False)
+    packed.check_status()
+    for r in runs[1:]:
+        assert torch.equal(r, runs[0])
+    assert torch.equal(y1, y2)
+    helpers.assert_close(runs[0], plain, rtol=1e-5, atol=1e-7, what="deterministic vs fp32-atomic accumulation")
+    helpers.assert_close(runs[0], o["rank_accum"], rtol=1e-2, atol=3e-4, what="deterministic mode vs fp32 oracle")
