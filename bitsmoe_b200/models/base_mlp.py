@@ -172,6 +172,17 @@ class BitsMoE_BaseMoeMLP(nn.Module):
     def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
         assign = bool(local_metadata.get("assign_to_params_buffers", False))
         consumed = []
+        # packer key schema (<prefix><mtype>.{u|vh}.payload_buffer ...): bind the tensors matrix by matrix
+        base = prefix[:-1] if prefix.endswith(".") else prefix
+        for mtype in self._MTYPE_TO_TAG:
+            keys = self._source_keys(state_dict, base, mtype)
+            if keys is None or keys["payload_buffer"] == f"{base}.{self._MTYPE_TO_TAG[mtype]}_payload_buffer":
+                continue
+            dev = state_dict[keys["payload_buffer"]].device
+            if self._load_one_mtype(state_dict, base, mtype, device=dev):
+                for k in keys.values():
+                    if k in state_dict:
+                        consumed.append(k)
         for leaf in self._runtime_buffer_leaf_keys():
             t = state_dict.get(f"{prefix}{leaf}", None)
             if not isinstance(t, torch.Tensor):

@@ -57,4 +57,7 @@ class BitsMoE_Qwen3MoeSparseMoeBlock(BitsMoE_BaseSparseMoeBlock):
             y = self._fused_forward(x, topk=(idx, w), residual=residual)
         else:
             y = self._fused_forward(x, logits=router_logits, residual=residual)
-        return y.reshape(batch, seq, hidden), router_logits
+        y = y.reshape(batch, seq, hidden)
+        # (hidden, router_logits) as the reference returns; hidden only where the surrounding decoder layer expects
+        # that (fused-expert models of transformers 5.x: the patcher clears the flag)
+        return (y, router_logits) if getattr(self, "return_router_logits", True) else y
