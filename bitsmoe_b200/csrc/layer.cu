@@ -436,7 +436,9 @@ static int basis_project_impl(const bm_layer_t* L, const void* x, int x_dtype, i
       a.zero_n = static_cast<int>(zero_bytes / 16);
       if (zeroed) *zeroed = true;
     }
-    return launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
+    const int rc = launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
+    if (rc != BM_ERR_UNSUPPORTED) return rc;
+    if (zeroed) *zeroed = false;       // shape does not tile (e.g. a very wide hidden size): the general GEMMs below take it
   }
   if (L->hidden % 64 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
     GemmTcArgs t{};
@@ -553,7 +555,8 @@ extern "C" int bm_combine_down_basis(const bm_layer_t* L, const float* rank_accu
     a.N = T; a.K = L->rank_out;
     a.x_dtype = BM_F32; a.c_dtype = y_dtype; a.round_x_f16 = 1;
     a.splits = 1; a.mrows = 16;
-    return launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
+    const int rc = launch_skinny_nt(a, static_cast<cudaStream_t>(stream));
+    if (rc != BM_ERR_UNSUPPORTED) return rc;
   }
   if (L->rank_out % 64 == 0) {
     GemmTcArgs t{};
