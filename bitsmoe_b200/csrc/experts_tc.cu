@@ -533,13 +533,17 @@ int launch_experts_tc(const bm_layer* L, const __half* h_gate, const __half* h_u
   BM_REQUIRE(L->max_slots <= 3 * 128, BM_ERR_UNSUPPORTED, "experts_tc: %d row slots exceed the tensor-memory budget", L->max_slots);
   const size_t smem = xt_smem_bytes(L->max_slots, L->max_words, L->num_experts);
   BM_REQUIRE(smem <= 224 * 1024, BM_ERR_UNSUPPORTED, "experts_tc: layer needs %zu bytes of shared memory", smem);
-  static int attr_set_for = -1;
-  static int sm_count = 148;
-  if (attr_set_for != L->device) {
+  static PerDeviceOnce attr_once;
+  static int sm_counts[MAX_DEVICES];
+  int dev = -1;
+  BM_CUDA(cudaGetDevice(&dev));
+  BM_REQUIRE(dev >= 0 && dev < MAX_DEVICES, BM_ERR_UNSUPPORTED, "experts_tc: device ordinal %d out of range", dev);
+  if (!attr_once.is_done(dev)) {
     BM_CUDA(cudaFuncSetAttribute(experts_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
-    BM_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, L->device));
-    attr_set_for = L->device;
+    BM_CUDA(cudaDeviceGetAttribute(&sm_counts[dev], cudaDevAttrMultiProcessorCount, dev));
+    attr_once.mark(dev);
   }
+  const int sm_count = sm_counts[dev];
   experts_tc_kernel<<<sm_count, XT_THREADS, smem, st>>>(
       L->fast_dev, static_cast<const unsigned char*>(L->arena), h_gate, h_up, L->rank_in, token_indices, expert_offsets,
       route_w, L->rank_out, T, L->num_experts, L->n_tiles, L->max_slots, L->max_words, rank_accum, acc64, L->status_dev);
