@@ -644,11 +644,13 @@ def ep_arm(args):
 
     def step(i, with_shared=True):
         j = i % L
-        res = shared_expert(xs[j], shared[j]) if with_shared else None
         if world == 1:
+            res = shared_expert(xs[j], shared[j]) if with_shared else None
             packed[j].forward(xs[j], lg[j], cfg.top_k, cfg.norm_topk_prob, torch.bfloat16, residual=res, out=ys[j], path=args.path)
         else:
-            sym[j].forward(xs[j], lg[j], torch.bfloat16, residual=res, out=ys[j], overlap=args.waves > 1)
+            # the shared expert runs on a side stream beside the exchange
+            fn = (lambda xw: shared_expert(xw, shared[j])) if with_shared else None
+            sym[j].forward(xs[j], lg[j], torch.bfloat16, out=ys[j], overlap=args.waves > 1, residual_fn=fn)
         return ys[j]
 
     # on-box parity of the expert-parallel step: rank 0 runs its own tokens through the whole layer on one GPU

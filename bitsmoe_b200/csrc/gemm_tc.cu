@@ -13,10 +13,11 @@
 
 namespace bm {
 
-constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_THREADS = 256, TC_STAGES = 4, TC_AHEAD = 3;
+constexpr int TC_BM = 128, TC_BK = 64, TC_THREADS = 256, TC_STAGES = 4, TC_AHEAD = 3;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KB
-constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;   // 32 KB
-constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+// The tile is 128 x BN with BN = 256, or 64 when the wide tile would leave most SMs without a CTA (few tokens and a
+// narrow output, e.g. the basis projection of 2048 tokens: 32 CTAs against 128).
+__host__ __device__ constexpr int tc_stage_bytes(int bn) { return TC_A_BYTES + bn * TC_BK * 2; }
 
 struct GemmTcArgs {
   const void* X;          // [M, K]
@@ -44,8 +45,9 @@ __device__ __forceinline__ uint32_t canon_off(int rows, int r, int kc) { return 
 // XD = BM_F16: activations go to shared memory untouched with cp.async.  XD = BM_BF16 / BM_F32: they are loaded
 // to registers (all loads of a slice first), rounded to fp16 and stored; both MMA operands are always fp16
 // (an instruction descriptor that mixed a bf16 A with an fp16 B raised "illegal instruction" on a B200).
-template <int XD>
+template <int XD, int TC_BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmTcArgs a) {
+  constexpr int TC_STAGE_BYTES = tc_stage_bytes(TC_BN);
   extern __shared__ __align__(1024) unsigned char tc_smem[];
   __shared__ __align__(8) uint64_t bar_free[TC_STAGES];   // MMAs that read stage s are complete
   __shared__ __align__(8) uint64_t bar_done;              // all MMAs of the tile are complete
@@ -182,16 +184,41 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(GemmTcArgs a) {
     // warp w reads TMEM lanes 32*(w%4).., columns 128*(w/4) .. +127
     const int row = m0 + 32 * (warp & 3) + lane;
     const int col_half = (warp >> 2) * (TC_BN / 2);
+    // N is a multiple of 8, so whole 16-byte accesses only need aligned bases
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(a.C[z]) | reinterpret_cast<uintptr_t>(a.residual)) & 15u) == 0;
 #pragma unroll 1
     for (int c = 0; c < TC_BN / 2; c += 32) {
       float v[32];
       tc::tmem_ld32(tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + col_half + c, v);
       const int n = n0 + col_half + c;
-      if (row < a.M && n + 32 <= a.N) {
+      if (row < a.M && n + 32 <= a.N && vec_ok) {
         const size_t idx = static_cast<size_t>(row) * a.N + n;
         if (a.residual && z == 0) {
+          // 16-byte loads: a lane owns 32 consecutive columns of its own row, so scalar loads would cost one
+          // memory instruction of 32 distinct sectors per column
+          if (a.c_dtype == BM_F32) {
+            const float4* rs = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.residual) + idx);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] += load_act(a.residual, a.c_dtype, idx + i);
+            for (int i = 0; i < 8; ++i) {
+              const float4 q = __ldg(rs + i);
+              v[4 * i] += q.x; v[4 * i + 1] += q.y; v[4 * i + 2] += q.z; v[4 * i + 3] += q.w;
+            }
+          } else {
+            const uint4* rs = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.residual) + idx);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 q = __ldg(rs + i);
+              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f;
+                if (a.c_dtype == BM_F16) f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                v[8 * i + 2 * j] += f.x;
+                v[8 * i + 2 * j + 1] += f.y;
+              }
+            }
+          }
         }
         if (a.c_dtype == BM_F32) {
 #pragma unroll
@@ -240,17 +267,31 @@ int launch_gemm_tc(const GemmTcArgs& a, int problems, cudaStream_t st) {
   static PerDeviceOnce attr_once;
   int dev = -1;
   BM_CUDA(cudaGetDevice(&dev));
-  const int smem = TC_STAGES * TC_STAGE_BYTES;
   if (!attr_once.is_done(dev)) {
-    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int big = TC_STAGES * tc_stage_bytes(256), small = TC_STAGES * tc_stage_bytes(64);
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_BF16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F32, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F16, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_BF16, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
+    BM_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BM_F32, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, small));
     attr_once.mark(dev);
   }
-  dim3 grid((a.M + TC_BM - 1) / TC_BM, (a.N + TC_BN - 1) / TC_BN, problems);
-  if (a.x_dtype == BM_F32) gemm_tc_kernel<BM_F32><<<grid, TC_THREADS, smem, st>>>(a);
-  else if (a.x_dtype == BM_BF16) gemm_tc_kernel<BM_BF16><<<grid, TC_THREADS, smem, st>>>(a);
-  else gemm_tc_kernel<BM_F16><<<grid, TC_THREADS, smem, st>>>(a);
+  const int mt = (a.M + TC_BM - 1) / TC_BM;
+  const bool narrow = mt * ((a.N + 255) / 256) * problems < 74;     // the wide tile would use fewer than half of the SMs
+  if (narrow) {
+    const int smem = TC_STAGES * tc_stage_bytes(64);
+    dim3 grid(mt, (a.N + 63) / 64, problems);
+    if (a.x_dtype == BM_F32) gemm_tc_kernel<BM_F32, 64><<<grid, TC_THREADS, smem, st>>>(a);
+    else if (a.x_dtype == BM_BF16) gemm_tc_kernel<BM_BF16, 64><<<grid, TC_THREADS, smem, st>>>(a);
+    else gemm_tc_kernel<BM_F16, 64><<<grid, TC_THREADS, smem, st>>>(a);
+  } else {
+    const int smem = TC_STAGES * tc_stage_bytes(256);
+    dim3 grid(mt, (a.N + 255) / 256, problems);
+    if (a.x_dtype == BM_F32) gemm_tc_kernel<BM_F32, 256><<<grid, TC_THREADS, smem, st>>>(a);
+    else if (a.x_dtype == BM_BF16) gemm_tc_kernel<BM_BF16, 256><<<grid, TC_THREADS, smem, st>>>(a);
+    else gemm_tc_kernel<BM_F16, 256><<<grid, TC_THREADS, smem, st>>>(a);
+  }
   BM_LAUNCH_CHECK("gemm_tc_kernel");
   return BM_OK;
 }

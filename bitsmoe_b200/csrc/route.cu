@@ -297,19 +297,36 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) route_scan_kernel(int32_t* __rest
   __shared__ int tot[ROUTE_MAX_E];
   __shared__ int off[ROUTE_MAX_E + 1];
   __shared__ int scratch[ROUTE_MAX_E + 1];
-  for (int x = threadIdx.x; x < E; x += blockDim.x) {
+  __shared__ int chunk_tot[ROUTE_BLOCK];
+  // The blocks' histograms are cut into `chunks` runs per expert, one thread each: every thread sums its run (independent
+  // loads), the runs' totals are combined in shared memory, and a second walk over the run writes the exclusive prefixes.
+  // One thread per expert walking all the blocks would serialise nblocks dependent round trips to memory.
+  const int chunks = max(1, min(static_cast<int>(blockDim.x) / E, nblocks));
+  const int len = (nblocks + chunks - 1) / chunks;
+  const int x = threadIdx.x % E, c = threadIdx.x / E;
+  const int b0 = c * len, b1 = min(nblocks, b0 + len);
+  const bool active = c < chunks;
+  if (active) {
+    int sum = 0;
+#pragma unroll 8
+    for (int b = b0; b < b1; ++b) sum += block_hist[static_cast<int64_t>(b) * E + x];
+    chunk_tot[c * E + x] = sum;
+  }
+  __syncthreads();
+  if (active) {
     int run = 0;
-#pragma unroll 4
-    for (int b = 0; b < nblocks; ++b) {
-      const int c = block_hist[static_cast<int64_t>(b) * E + x];
+    for (int cc = 0; cc < c; ++cc) run += chunk_tot[cc * E + x];
+    if (c == chunks - 1) tot[x] = run + chunk_tot[c * E + x];
+#pragma unroll 8
+    for (int b = b0; b < b1; ++b) {
+      const int v = block_hist[static_cast<int64_t>(b) * E + x];
       block_hist[static_cast<int64_t>(b) * E + x] = run;
-      run += c;
+      run += v;
     }
-    tot[x] = run;
   }
   __syncthreads();
   block_exclusive_scan(tot, off, E);
-  for (int x = threadIdx.x; x <= E; x += blockDim.x) expert_offsets[x] = off[x];
+  for (int i = threadIdx.x; i <= E; i += blockDim.x) expert_offsets[i] = off[i];
   write_tile_table(off, E, tile_rows, tile_table, max_tiles, counts, scratch, tot);
 }
 

@@ -342,6 +342,7 @@ class SymmetricExpertParallel:
                 ws=torch.empty(max(self._ws_bytes, 256), dtype=torch.uint8, device=dev),
                 acc=torch.empty((T, r_out), dtype=torch.float32, device=dev)))
         self.streams = [torch.cuda.Stream(device=dev) for _ in range(self.AREAS)]
+        self._side = [torch.cuda.Stream(device=dev) for _ in range(self.AREAS)]
         torch.cuda.synchronize(dev)          # the zeroed flag area is in place before any peer signals into it
         dist.barrier(group=self.group)
 
@@ -365,8 +366,11 @@ class SymmetricExpertParallel:
         return push, rows * self.packed.rank_out * 4
 
     def forward_wave(self, x: torch.Tensor, logits: torch.Tensor, weight_dtype, out: torch.Tensor,
-                     residual: Optional[torch.Tensor] = None, area: int = 0) -> torch.Tensor:
-        """One wave on the current stream: x [T, H], logits [T, E] of this rank's tokens -> out [T, H]."""
+                     residual: Optional[torch.Tensor] = None, area: int = 0, residual_fn=None) -> torch.Tensor:
+        """One wave on the current stream: x [T, H], logits [T, E] of this rank's tokens -> out [T, H].
+
+        ``residual_fn(x) -> [T, H]`` (e.g. a dense shared expert) runs on a side stream beside the exchange and the
+        barriers, where the GPU is mostly idle; the wave waits for it only before the final down-basis product."""
         capi, lib, pk = self._capi, self._capi.lib(), self.packed
         G, T, k, r, r_out = self.world, self.T, self.top_k, pk.rank_in, pk.rank_out
         if x.shape[0] != T:
@@ -377,6 +381,12 @@ class SymmetricExpertParallel:
         st = capi.stream_ptr(pk.device)
         x, logits = x.contiguous(), logits.contiguous()
         with torch.cuda.device(pk.device):
+            if residual_fn is not None:
+                main, side = torch.cuda.current_stream(pk.device), self._side[area]
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    residual = residual_fn(x)
+                    residual.record_stream(main)
             idx_mine, w_mine = rt[0, self.rank], rt[1, self.rank]
             capi.check(lib.bm_route_topk(logits.data_ptr(), capi.dtype_code(logits.dtype), T, logits.shape[1], k,
                                          int(bool(self.norm_topk_prob)), capi.round_code(weight_dtype), idx_mine.data_ptr(),
@@ -397,7 +407,11 @@ class SymmetricExpertParallel:
             capi.check(lib.bm_ep_barrier(pk._handle, self._flags, G, self.rank, 2 * area + 1, self.barrier_limit_ms, st))
             capi.check(lib.bm_ep_pull_reduce(p_tab, idx_mine.data_ptr(), G, self.rank, T, r_out, k, self.per,
                                              sc["acc"].data_ptr(), st))
-            if residual is not None:
+            if residual_fn is not None:
+                with torch.cuda.stream(side):
+                    residual = residual.to(x.dtype).contiguous()
+                main.wait_stream(side)
+            elif residual is not None:
                 residual = residual.to(x.dtype).contiguous()
             capi.check(lib.bm_combine_down_basis(pk._handle, sc["acc"].data_ptr(), T, capi.ptr(residual), out.data_ptr(),
                                                  capi.dtype_code(out.dtype), st))
@@ -405,9 +419,10 @@ class SymmetricExpertParallel:
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, weight_dtype=torch.float16,
                 residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                overlap: bool = True) -> torch.Tensor:
+                overlap: bool = True, residual_fn=None) -> torch.Tensor:
         """x [n*T, H] -> y [n*T, H] in n waves of T tokens; with ``overlap`` consecutive waves alternate between two
-        streams (and two receive areas), so one wave's exchange runs beside the other's expert kernel."""
+        streams (and two receive areas), so one wave's exchange runs beside the other's expert kernel.
+        ``residual_fn``: see ``forward_wave`` (called once per wave with that wave's rows of ``x``)."""
         T = self.T
         if x.shape[0] % T:
             raise ValueError(f"{x.shape[0]} tokens are not a whole number of waves of {T}")
@@ -417,14 +432,16 @@ class SymmetricExpertParallel:
         if not overlap or n == 1:
             for w in range(n):
                 s = slice(w * T, (w + 1) * T)
-                self.forward_wave(x[s], logits[s], weight_dtype, y[s], None if residual is None else residual[s], area=w % self.AREAS)
+                self.forward_wave(x[s], logits[s], weight_dtype, y[s], None if residual is None else residual[s], area=w % self.AREAS,
+                                  residual_fn=residual_fn)
             return y
         for st in self.streams:
             st.wait_stream(cur)
         for w in range(n):
             s = slice(w * T, (w + 1) * T)
             with torch.cuda.stream(self.streams[w % self.AREAS]):
-                self.forward_wave(x[s], logits[s], weight_dtype, y[s], None if residual is None else residual[s], area=w % self.AREAS)
+                self.forward_wave(x[s], logits[s], weight_dtype, y[s], None if residual is None else residual[s], area=w % self.AREAS,
+                                  residual_fn=residual_fn)
         for st in self.streams:
             cur.wait_stream(st)
         return y

@@ -22,10 +22,10 @@ def _config():
         max_position_embeddings=64, decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True, hidden_act="silu")
 
 
-def _checkpoint(cfg):
+def _checkpoint(cfg, super_map=SUPER):
     """A BitsMoE checkpoint for the tiny model: the stock model's dense tensors (attention, norms, embeddings, router),
     plus per MoE layer the three basis buffers and every expert's packed buffers in the packer's key schema; expert 3
-    of layer 1 stays dense ("super")."""
+    of layer 1 stays dense ("super") under the default ``super_map``."""
     torch.manual_seed(0)
     stock = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.float16)
     state = {k: v.clone() for k, v in stock.state_dict().items() if ".mlp.experts." not in k}
@@ -38,7 +38,7 @@ def _checkpoint(cfg):
         state[f"{pre}.shared_vh_gate_proj"], state[f"{pre}.shared_vh_up_proj"] = layer.vh_gate, layer.vh_up
         state[f"{pre}.shared_u_down"] = layer.u_down
         for e in range(NEXP):
-            if e in SUPER.get(li, []):
+            if e in super_map.get(li, []):
                 gu, dn = stock.model.layers[li].mlp.experts.gate_up_proj[e], stock.model.layers[li].mlp.experts.down_proj[e]
                 state[f"{pre}.experts.{e}.gate_proj.weight"] = gu[:INTER].detach().clone()
                 state[f"{pre}.experts.{e}.up_proj.weight"] = gu[INTER:].detach().clone()
@@ -77,12 +77,31 @@ def test_patcher_rewrites_fused_expert_blocks_and_loads_the_checkpoint():
         patch_bitsmoe_inplace(stock2, "mixtral")
 
 
+def _oracle_block(x2, logits, layer, dense):
+    """The block's output on the CPU: packed experts through the oracle; an expert listed in ``dense`` (id -> its three
+    matrices) acts as a plain MLP on its tokens instead."""
+    idx, w = oforward.router(logits, TOPK, True, torch.float16)
+    w_packed = w.clone()
+    for e in dense:
+        w_packed[idx == e] = 0.0
+    tok, off, rw = oforward.build_routing(idx, w_packed, NEXP)
+    hg, hu = oforward.basis_project(x2, layer.vh_gate), oforward.basis_project(x2, layer.vh_up)
+    acc = oforward.packed_forward(hg, hu, tok, off, rw, helpers.decoded_experts(layer), layer.u_down.shape[1])
+    y = oforward.down_basis(acc, layer.u_down, torch.float32)
+    for e, (wg, wu, wd) in dense.items():
+        rows, slots = (idx == e).nonzero(as_tuple=True)
+        if rows.numel():
+            y[rows] += w[rows, slots].float()[:, None] * oforward.dense_mlp(x2[rows], wg, wu, wd).float()
+    return y
+
+
 @pytest.mark.gpu
-def test_patched_model_runs_and_its_blocks_match_the_oracle():
+@pytest.mark.parametrize("super_map", [{}, SUPER], ids=["all-packed", "one-dense-expert"])
+def test_patched_model_runs_and_its_blocks_match_the_oracle(super_map):
     cfg = _config()
-    _, state, layers = _checkpoint(cfg)
+    _, state, layers = _checkpoint(cfg, super_map)
     dev = torch.device("cuda", 0)
-    model = build_patched_model(cfg, "qwen3moe", state, device=dev, super_experts_by_layer={})   # all experts packed
+    model = build_patched_model(cfg, "qwen3moe", state, device=dev, super_experts_by_layer=super_map)
     model.eval()
     seen = {}
     hooks = [model.model.layers[li].mlp.register_forward_hook(lambda mod, inp, out, li=li: seen.__setitem__(li, (inp[0].detach(), out.detach())))
@@ -98,7 +117,8 @@ def test_patched_model_runs_and_its_blocks_match_the_oracle():
         x2 = x.reshape(-1, HID).cpu()
         blk = model.model.layers[li].mlp
         logits = (x2.double() @ blk.gate.weight.detach().cpu().double().T).to(torch.float16)
-        o = oforward.layer_forward(x2, logits.float(), layers[li].vh_gate, layers[li].vh_up, layers[li].u_down,
-                                   helpers.decoded_experts(layers[li]), TOPK, True, torch.float16)
-        helpers.assert_close(y.reshape(-1, HID), o["y_fp32"], what=f"patched model, MoE block of layer {li}")
-        helpers.assert_detects_damage(y.reshape(-1, HID), o["y_fp32"])
+        dense = {e: tuple(state[f"model.layers.{li}.mlp.experts.{e}.{m}.weight"] for m in ("gate_proj", "up_proj", "down_proj"))
+                 for e in super_map.get(li, [])}
+        want = _oracle_block(x2, logits.float(), layers[li], dense)
+        helpers.assert_close(y.reshape(-1, HID), want, what=f"patched model, MoE block of layer {li}")
+        helpers.assert_detects_damage(y.reshape(-1, HID), want)
