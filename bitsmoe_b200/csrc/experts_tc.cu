@@ -331,12 +331,15 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
             const uint4 sv = *reinterpret_cast<const uint4*>(sm.s_r + r0);
             const int dst[8] = {static_cast<int>(d0.x), static_cast<int>(d0.y), static_cast<int>(d0.z), static_cast<int>(d0.w),
                                 static_cast<int>(d1.x), static_cast<int>(d1.y), static_cast<int>(d1.z), static_cast<int>(d1.w)};
-            const __half* hp = reinterpret_cast<const __half*>(&hv[u]);
-            const __half* sp = reinterpret_cast<const __half*>(&sv);
+            const __half2* hp = reinterpret_cast<const __half2*>(&hv[u]);
+            const __half2* sp = reinterpret_cast<const __half2*>(&sv);
             unsigned char* row = sm.act + mm[u] * act_m_bytes + (nn[u] >> 3) * 128 + (nn[u] & 7) * 16;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (dst[j] >= 0) *reinterpret_cast<__half*>(row + dst[j]) = __float2half_rn(__half2float(hp[j]) * __half2float(sp[j]));
+            for (int j = 0; j < 4; ++j) {
+              const __half2 pr = __hmul2(hp[j], sp[j]);       // one rounding of the exact product, as fp16(h * s)
+              if (dst[2 * j] >= 0) *reinterpret_cast<__half*>(row + dst[2 * j]) = __low2half(pr);
+              if (dst[2 * j + 1] >= 0) *reinterpret_cast<__half*>(row + dst[2 * j + 1]) = __high2half(pr);
+            }
           }
         }
       }
@@ -371,7 +374,8 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
       // ------------------------------------------------------------------ MMA issue, one thread per pipeline
       // pipeline 0: gate products and the down product's even row tiles; pipeline 1: up products and the odd row tiles
       const int pl = warp - XT_MMA_WARP0;
-      if (lane == 0) {
+      // The whole warp waits (a lone waiting lane wakes up several times slower); lane 0 issues.
+      {
         bool ok = xt_wait(&bars.act_ready, item_round & 1, abort_flag);
         const uint32_t act_m_bytes = static_cast<uint32_t>(max_slots / 8) * cs;
         // descriptors: constant upper part, start-address field advanced per block
@@ -389,16 +393,20 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
             const uint32_t d_acc = tmem_base + (2 * b + pl) * acc_stride;
             for (int kb0 = 0; kb0 < nkb && ok; kb0 += XT_STAGE_BLOCKS) {
               if (!(ok = xt_wait(&w_full[ring_c.i], ring_c.ph, abort_flag))) break;
-              const int cnt = min(XT_STAGE_BLOCKS, nkb - kb0);
-              const uint64_t ad = a_desc0 + ((ring_c.i * XT_STAGE_BYTES) >> 4);
-              const uint64_t bd = b_desc0 + ((2 * kb0 * cs) >> 4);
-              for (int j = 0; j < cnt; ++j)
-                tc::mma_f16(d_acc, ad + ((2 * j * XT_A_CHUNK) >> 4), bd + ((2 * j * cs) >> 4), idesc, (kb0 + j) > 0 ? 1u : 0u);
-              tc::mma_commit(&w_empty[ring_c.i]);
+              if (lane == 0) {
+                const int cnt = min(XT_STAGE_BLOCKS, nkb - kb0);
+                const uint64_t ad = a_desc0 + ((ring_c.i * XT_STAGE_BYTES) >> 4);
+                const uint64_t bd = b_desc0 + ((2 * kb0 * cs) >> 4);
+                for (int j = 0; j < cnt; ++j)
+                  tc::mma_f16(d_acc, ad + ((2 * j * XT_A_CHUNK) >> 4), bd + ((2 * j * cs) >> 4), idesc, (kb0 + j) > 0 ? 1u : 0u);
+                tc::mma_commit(&w_empty[ring_c.i]);
+              }
+              __syncwarp();
               ring_c.next(ring_h);
             }
             if (!ok) break;
-            tc::mma_commit(&bars.gu_done[b]);
+            if (lane == 0) tc::mma_commit(&bars.gu_done[b]);
+            __syncwarp();
           }
           if (t > 0) {
             const int tile = t - 1;
@@ -409,19 +417,23 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
             for (int mt = pl; mt < n_mt && ok; mt += 2) {
               for (int kb0 = 0; kb0 < 8; kb0 += XT_STAGE_BLOCKS) {
                 if (!(ok = xt_wait(&w_full[ring_c.i], ring_c.ph, abort_flag))) break;
-                const uint64_t ad = a_desc0 + ((ring_c.i * XT_STAGE_BYTES) >> 4);
-                const uint64_t bd = zd + ((2 * kb0 * cs) >> 4);
-                for (int j = 0; j < XT_STAGE_BLOCKS; ++j)
-                  tc::mma_f16(d_down + mt * acc_stride, ad + ((2 * j * XT_A_CHUNK) >> 4), bd + ((2 * j * cs) >> 4), idesc,
-                              (tile > 0 || kb0 + j > 0) ? 1u : 0u);
-                tc::mma_commit(&w_empty[ring_c.i]);
+                if (lane == 0) {
+                  const uint64_t ad = a_desc0 + ((ring_c.i * XT_STAGE_BYTES) >> 4);
+                  const uint64_t bd = zd + ((2 * kb0 * cs) >> 4);
+                  for (int j = 0; j < XT_STAGE_BLOCKS; ++j)
+                    tc::mma_f16(d_down + mt * acc_stride, ad + ((2 * j * XT_A_CHUNK) >> 4), bd + ((2 * j * cs) >> 4), idesc,
+                                (tile > 0 || kb0 + j > 0) ? 1u : 0u);
+                  tc::mma_commit(&w_empty[ring_c.i]);
+                }
+                __syncwarp();
                 ring_c.next(ring_h);
               }
             }
-            if (ok) {
+            if (ok && lane == 0) {
               tc::mma_commit(&bars.z_free[zb]);
               if (t == n_tiles) tc::mma_commit(&bars.down_done);
             }
+            __syncwarp();
           }
         }
       }
@@ -579,22 +591,49 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         const FastMat& fd = fe.m[2];
         const int16_t* rank_d = reinterpret_cast<const int16_t*>(arena + fd.tab_off);
         const __half* s_d = reinterpret_cast<const __half*>(arena + fd.tab_off + fd.nslots * 2);
-        for (int mt = 0; mt < n_mt; ++mt) {
-          const int slot = 128 * mt + 32 * q + lane;
-          int rk = -1;
-          float sv = 0.f;
-          if (slot < fd.nslots) { rk = rank_d[slot]; sv = __half2float(s_d[slot]); }
-          const bool live = rk >= 0 && rk < rank_out;
-          for (int n0 = n_first; n0 < n_mma; n0 += 64) {
+        // A thread owns a row slot, and the slots of a warp map to scattered ranks: adding straight from the registers
+        // costs one 32-byte sector per lane and instruction.  With room for it (the operand ring is idle by now) the
+        // four warps that share a 32-token chunk transpose it through shared memory and add whole rows, 16 bytes per
+        // lane; ranks without a slot add zero.
+        const int grp = warp >> 2;
+        const bool transpose = acc64 == nullptr && (rank_out & 3) == 0 &&
+                               static_cast<size_t>(2) * 32 * rank_out * 4 <= static_cast<size_t>(2 * ring_h) * XT_STAGE_BYTES;
+        float* tbuf = reinterpret_cast<float*>(sm.ring) + grp * 32 * rank_out;
+        for (int n0 = n_first; n0 < n_mma; n0 += 64) {
+          if (transpose) {
+            for (int i = (warp & 3) * 32 + lane; i < 8 * rank_out; i += 128) reinterpret_cast<float4*>(tbuf)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+          }
+          for (int mt = 0; mt < n_mt; ++mt) {
+            const int slot = 128 * mt + 32 * q + lane;
+            int rk = -1;
+            float sv = 0.f;
+            if (slot < fd.nslots) { rk = rank_d[slot]; sv = __half2float(s_d[slot]); }
+            const bool live = rk >= 0 && rk < rank_out;
             float v[32];
             tc::tmem_ld32(d_down + mt * acc_stride + lane_sel + n0, v);
             if (live) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 const int n = n0 + i;
-                if (n < n_tok) acc_add(rank_accum, acc64, static_cast<int64_t>(item.tok[n]) * rank_out + rk, v[i] * sv * item.rw[n]);
+                if (n < n_tok) {
+                  const float val = v[i] * sv * item.rw[n];
+                  if (transpose) tbuf[i * rank_out + rk] = val;
+                  else acc_add(rank_accum, acc64, static_cast<int64_t>(item.tok[n]) * rank_out + rk, val);
+                }
               }
             }
+          }
+          if (transpose) {
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+            for (int i = q; i < 32 && n0 + i < n_tok; i += 4) {
+              float* dst = rank_accum + static_cast<int64_t>(item.tok[n0 + i]) * rank_out;
+              for (int c0 = lane * 4; c0 < rank_out; c0 += 128) {
+                const float4 x = *reinterpret_cast<const float4*>(tbuf + i * rank_out + c0);
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + c0), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w) : "memory");
+              }
+            }
+            if (n0 + 64 < n_mma) asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
           }
         }
         tc::fence_before_sync();
