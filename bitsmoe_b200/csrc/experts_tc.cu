@@ -570,14 +570,20 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         const uint32_t d_gate = tmem_base + 2 * b * acc_stride, d_up = d_gate + acc_stride;
         unsigned char* zr = zrow + b * z_bytes;
         for (int n0 = n_first; n0 < n_mma; n0 += 64) {
-          float gv[32], uv[32];
-          tc::tmem_ld32(d_gate + lane_sel + n0, gv);
-          tc::tmem_ld32(d_up + lane_sel + n0, uv);
+          // 16 columns at a time: two 32-column loads would hold 64 registers per thread
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int n = n0 + i;
-            const float zf = __fdividef(gv[i] * uv[i], 1.f + __expf(-gv[i]));
-            if (n < n_mma) *reinterpret_cast<__half*>(zr + (n >> 3) * 128 + (n & 7) * 16) = __float2half_rn(n < n_tok ? zf : 0.f);
+          for (int hh = 0; hh < 2; ++hh) {
+            const int nb = n0 + 16 * hh;
+            if (nb >= n_mma) break;
+            float gv[16], uv[16];
+            tc::tmem_ld16(d_gate + lane_sel + nb, gv);
+            tc::tmem_ld16(d_up + lane_sel + nb, uv);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int n = nb + i;
+              const float zf = __fdividef(gv[i] * uv[i], 1.f + __expf(-gv[i]));
+              *reinterpret_cast<__half*>(zr + (n >> 3) * 128 + (n & 7) * 16) = __float2half_rn(n < n_tok ? zf : 0.f);
+            }
           }
         }
         tc::fence_before_sync();
@@ -610,16 +616,21 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
             float sv = 0.f;
             if (slot < fd.nslots) { rk = rank_d[slot]; sv = __half2float(s_d[slot]); }
             const bool live = rk >= 0 && rk < rank_out;
-            float v[32];
-            tc::tmem_ld32(d_down + mt * acc_stride + lane_sel + n0, v);
-            if (live) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const int n = n0 + i;
-                if (n < n_tok) {
-                  const float val = v[i] * sv * item.rw[n];
-                  if (transpose) tbuf[i * rank_out + rk] = val;
-                  else acc_add(rank_accum, acc64, static_cast<int64_t>(item.tok[n]) * rank_out + rk, val);
+            for (int hh = 0; hh < 2; ++hh) {
+              const int nb = n0 + 16 * hh;
+              if (nb >= n_mma) break;
+              float v[16];
+              tc::tmem_ld16(d_down + mt * acc_stride + lane_sel + nb, v);
+              if (live) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const int n = nb + i;
+                  if (n < n_tok) {
+                    const float val = v[i] * sv * item.rw[n];
+                    if (transpose) tbuf[(16 * hh + i) * rank_out + rk] = val;
+                    else acc_add(rank_accum, acc64, static_cast<int64_t>(item.tok[n]) * rank_out + rk, val);
+                  }
                 }
               }
             }
