@@ -278,17 +278,22 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
       const int tid_s = warp < XT_EPI_WARPS ? threadIdx.x : threadIdx.x - (XT_DQ_WARP0 - XT_EPI_WARPS) * 32;
       const uint32_t act_m_bytes = static_cast<uint32_t>(max_slots / 8) * cs;
       // act[m][chunk][n] = 8 consecutive contraction positions of token n: fp16(h[token, rank(slot)] * s(slot)).
-      // The rows of h are read whole, in rank order (16 bytes per thread, a row per warp), and every value is stored
-      // where its row slot sits in the operand; reading in slot order instead would touch every 32-byte sector of a
-      // row eight times.  Two tables per matrix, indexed by rank: where the value goes (or -1) and its factor.
-      for (int i = tid_s; i < 2 * h_rank; i += XT_STAGERS) sm.dst_r[i] = -1;
-      for (int i = tid_s; i < 2 * h_rank; i += XT_STAGERS) sm.s_r[i] = __float2half(0.f);
+      // A warp takes a token; its lanes read consecutive ranks of the row (reading in slot order instead would touch
+      // every 32-byte sector of a row eight times) and store every value where its row slot sits in the operand.
+      // Consecutive ranks sit at mostly consecutive positions, so the lanes' 2-byte stores fall into distinct banks.
+      // Two tables per matrix, indexed by rank: where the value goes (or -1) and its factor.
+      const int warp_s = tid_s >> 5;
+      for (int i = tid_s; i < 2 * h_rank; i += XT_STAGERS) {
+        sm.dst_r[i] = -1;
+        sm.s_r[i] = __float2half(0.f);
+      }
       // rows 0 .. n_mma - 1 of every chunk start as zero (padding slots, rows past the item's tokens)
-      const int nch_all = (fe.m[0].nslots + fe.m[1].nslots) >> 3, nch0 = fe.m[0].nslots >> 3;
-      for (int i = tid_s; i < nch_all * n_mma; i += XT_STAGERS) {
-        const int c8 = i / n_mma, n = i - c8 * n_mma;
-        const int m = c8 >= nch0 ? 1 : 0, cm = c8 - m * nch0;
-        *reinterpret_cast<uint4*>(sm.act + m * act_m_bytes + cm * cs + n * 16) = make_uint4(0, 0, 0, 0);
+      {
+        const int nch0 = fe.m[0].nslots >> 3, nch_all = nch0 + (fe.m[1].nslots >> 3);
+        for (int c8 = warp_s; c8 < nch_all; c8 += XT_STAGERS / 32) {
+          unsigned char* chunk = sm.act + (c8 >= nch0 ? act_m_bytes + (c8 - nch0) * cs : c8 * cs);
+          for (int n = lane; n < n_mma; n += 32) *reinterpret_cast<uint4*>(chunk + n * 16) = make_uint4(0, 0, 0, 0);
+        }
       }
       asm volatile("bar.sync 1, %0;" ::"n"(XT_STAGERS) : "memory");
       for (int m = 0; m < 2; ++m) {
@@ -305,40 +310,36 @@ __global__ void __launch_bounds__(XT_THREADS, 1) experts_tc_kernel(
         }
       }
       asm volatile("bar.sync 1, %0;" ::"n"(XT_STAGERS) : "memory");
-      {
-        const int vecs = h_rank >> 3, total = 2 * n_tok * vecs;       // tasks: (matrix, token, 8 consecutive ranks)
-        for (int base = tid_s; base < total; base += 4 * XT_STAGERS) {
-          uint4 hv[4];
-          int mm[4], nn[4], vv[4];
+      for (int m = 0; m < 2; ++m) {
+        const __half* h = m == 0 ? h_gate : h_up;
+        for (int r0 = 0; r0 < h_rank; r0 += 256) {        // lane l takes the ranks r0 + l + 32 k
+          int dst[8];
+          __half sc[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int task = base + u * XT_STAGERS;
-            mm[u] = -1;
-            if (task < total) {
-              const int row = task / vecs;
-              vv[u] = task - row * vecs;
-              mm[u] = row >= n_tok ? 1 : 0;
-              nn[u] = row - mm[u] * n_tok;
-              const __half* hrow = (mm[u] ? h_up : h_gate) + static_cast<int64_t>(item.tok[nn[u]]) * h_rank;
-              hv[u] = *reinterpret_cast<const uint4*>(hrow + vv[u] * 8);
-            }
+          for (int k = 0; k < 8; ++k) {
+            const int r = r0 + lane + 32 * k;
+            dst[k] = r < h_rank ? sm.dst_r[m * h_rank + r] : -1;
+            sc[k] = r < h_rank ? sm.s_r[m * h_rank + r] : __float2half(0.f);
           }
+          for (int n = warp_s; n < n_tok; n += 2 * (XT_STAGERS / 32)) {
+            // two tokens per round: sixteen loads in flight per lane
+            const int n2 = n + XT_STAGERS / 32;
+            const __half* row0 = h + static_cast<int64_t>(item.tok[n]) * h_rank + r0 + lane;
+            const __half* row1 = h + static_cast<int64_t>(item.tok[n2 < n_tok ? n2 : n]) * h_rank + r0 + lane;
+            __half hv0[8], hv1[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (mm[u] < 0) continue;
-            const int r0 = mm[u] * h_rank + vv[u] * 8;
-            const uint4 d0 = *reinterpret_cast<const uint4*>(sm.dst_r + r0), d1 = *reinterpret_cast<const uint4*>(sm.dst_r + r0 + 4);
-            const uint4 sv = *reinterpret_cast<const uint4*>(sm.s_r + r0);
-            const int dst[8] = {static_cast<int>(d0.x), static_cast<int>(d0.y), static_cast<int>(d0.z), static_cast<int>(d0.w),
-                                static_cast<int>(d1.x), static_cast<int>(d1.y), static_cast<int>(d1.z), static_cast<int>(d1.w)};
-            const __half2* hp = reinterpret_cast<const __half2*>(&hv[u]);
-            const __half2* sp = reinterpret_cast<const __half2*>(&sv);
-            unsigned char* row = sm.act + mm[u] * act_m_bytes + (nn[u] >> 3) * 128 + (nn[u] & 7) * 16;
+            for (int k = 0; k < 8; ++k) {
+              hv0[k] = dst[k] >= 0 ? row0[32 * k] : __float2half(0.f);
+              hv1[k] = dst[k] >= 0 ? row1[32 * k] : __float2half(0.f);
+            }
+            unsigned char* out0 = sm.act + m * act_m_bytes + (n >> 3) * 128 + (n & 7) * 16;
+            unsigned char* out1 = sm.act + m * act_m_bytes + (n2 >> 3) * 128 + (n2 & 7) * 16;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const __half2 pr = __hmul2(hp[j], sp[j]);       // one rounding of the exact product, as fp16(h * s)
-              if (dst[2 * j] >= 0) *reinterpret_cast<__half*>(row + dst[2 * j]) = __low2half(pr);
-              if (dst[2 * j + 1] >= 0) *reinterpret_cast<__half*>(row + dst[2 * j + 1]) = __high2half(pr);
+            for (int k = 0; k < 8; ++k) {
+              if (dst[k] >= 0) {
+                *reinterpret_cast<__half*>(out0 + dst[k]) = __hmul(hv0[k], sc[k]);      // one rounding of the exact product
+                if (n2 < n_tok) *reinterpret_cast<__half*>(out1 + dst[k]) = __hmul(hv1[k], sc[k]);
+              }
             }
           }
         }
