@@ -158,6 +158,25 @@ struct GemmArgs {
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 __host__ __device__ inline size_t align_up_c(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Arguments of the tensor-core basis products (gemm_tma.cu, gemm_tc.cu): C[z] = X . W[z]^T (+ residual for z = 0).
+struct GemmTcArgs {
+  const void* X;          // [M, K]
+  const __half* W[2];     // [N, K] each
+  void* C[2];             // [M, N] each
+  const void* residual;   // [M, N] (W[0] only) or null
+  int M, N, K;
+  int x_dtype, c_dtype;
+  int* status;
+};
+// Tiled-copy kernel first; BM_ERR_UNSUPPORTED (nothing launched) means: use launch_gemm_tc.
+int launch_gemm_tma(const GemmTcArgs& a, int problems, cudaStream_t st);
+int launch_gemm_tc(const GemmTcArgs& a, int problems, cudaStream_t st);
+// Both in order.
+inline int launch_gemm_basis(const GemmTcArgs& a, int problems, cudaStream_t st) {
+  const int rc = launch_gemm_tma(a, problems, st);
+  return rc == BM_ERR_UNSUPPORTED ? launch_gemm_tc(a, problems, st) : rc;
+}
+
 }  // namespace bm
 
 struct bm_layer {

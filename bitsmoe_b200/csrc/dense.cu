@@ -23,16 +23,6 @@ struct SkinnyArgs {
   int zero_n;
 };
 int launch_skinny_nt(SkinnyArgs a, cudaStream_t st);
-struct GemmTcArgs {
-  const void* X;
-  const __half* W[2];
-  void* C[2];
-  const void* residual;
-  int M, N, K;
-  int x_dtype, c_dtype;
-  int* status;
-};
-int launch_gemm_tc(const GemmTcArgs& a, int problems, cudaStream_t st);
 int launch_gemm_nt(const GemmArgs& g, int problems, cudaStream_t st);
 
 constexpr int DENSE_SKINNY_MAX_TOKENS = 256;
@@ -67,7 +57,7 @@ int dense_xwT(const void* X, int x_dtype, const __half* W0, const __half* W1, vo
     GemmTcArgs t{};
     t.X = X; t.W[0] = W0; t.W[1] = problems > 1 ? W1 : W0; t.C[0] = C0; t.C[1] = problems > 1 ? C1 : C0;
     t.residual = residual; t.M = T; t.N = N; t.K = K; t.x_dtype = x_dtype; t.c_dtype = c_dtype; t.status = status;
-    return launch_gemm_tc(t, problems, st);
+    return launch_gemm_basis(t, problems, st);
   }
   GemmArgs g{};
   g.A[0] = g.A[1] = X;

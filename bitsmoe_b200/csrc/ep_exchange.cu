@@ -26,52 +26,48 @@ struct EpPeers {
   void* p[EP_MAX_WORLD];
 };
 
-// One warp per local token.
+// One warp per (local token, destination rank): the stores to one peer are independent of those to the others, and
+// a warp per pair keeps seven times as many of them in flight as a warp that walks the destinations.
 __global__ void __launch_bounds__(256) ep_push_kernel(EpPeers H, EpPeers R, int world, int rank, int T, int r, int k,
                                                       int experts_per_rank) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= T) return;
+  const int pair = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int t = pair / world, d = pair - t * world;
+  if (t >= T || d == rank) return;
   const size_t GT = static_cast<size_t>(world) * T;
   const size_t u = static_cast<size_t>(rank) * T + t;
   const int32_t* my_idx = reinterpret_cast<const int32_t*>(R.p[rank]) + u * k;
   const int32_t* my_w = reinterpret_cast<const int32_t*>(R.p[rank]) + (GT + u) * k;
-  // destinations of this token: owners of its experts
+  // does rank d own one of the token's experts?
   unsigned need = 0;
-  int32_t id = -1, wbits = 0;
   if (lane < k) {
-    id = my_idx[lane];
-    wbits = my_w[lane];
-    const int d = id >= 0 ? id / experts_per_rank : -1;
-    if (d >= 0 && d < world) need = 1u << d;
+    const int32_t id = my_idx[lane];
+    // routing of every token goes to every rank (its routing build walks all tokens of the wave)
+    reinterpret_cast<int32_t*>(R.p[d])[u * k + lane] = id;
+    reinterpret_cast<int32_t*>(R.p[d])[(GT + u) * k + lane] = my_w[lane];
+    need = id >= 0 && id / experts_per_rank == d ? 1u : 0u;
   }
-  need = __reduce_or_sync(0xffffffffu, need);
+  if (!__any_sync(0xffffffffu, need)) return;
   const uint4* src_g = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(H.p[rank]) + u * r);
   const uint4* src_u = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(H.p[rank]) + (GT + u) * r);
-  const int vec = r / 8;
-  for (int d = 0; d < world; ++d) {
-    if (d == rank) continue;
-    // routing of every token goes to every rank (its routing build walks all tokens of the wave)
-    if (lane < k) {
-      reinterpret_cast<int32_t*>(R.p[d])[u * k + lane] = id;
-      reinterpret_cast<int32_t*>(R.p[d])[(GT + u) * k + lane] = wbits;
-    }
-    if (!((need >> d) & 1u)) continue;
-    uint4* dst_g = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(H.p[d]) + u * r);
-    uint4* dst_u = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(H.p[d]) + (GT + u) * r);
-    for (int i = lane; i < vec; i += 32) {
-      dst_g[i] = src_g[i];
-      dst_u[i] = src_u[i];
-    }
+  uint4* dst_g = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(H.p[d]) + u * r);
+  uint4* dst_u = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(H.p[d]) + (GT + u) * r);
+  for (int i = lane; i < r / 8; i += 32) {
+    dst_g[i] = src_g[i];
+    dst_u[i] = src_u[i];
   }
 }
 
-// One warp per local token: rank_accum[t] = sum over the ranks that own one of its experts of their partial row.
+// One warp per (local token, 128 values of the row): rank_accum[t] = sum over the ranks that own one of its experts of
+// their partial row, in ascending rank order.  All peer loads of a warp are issued before the first is used: a load from
+// a peer takes microseconds, and one after the other they would add up.
 __global__ void __launch_bounds__(256) ep_pull_reduce_kernel(EpPeers PART, const int32_t* __restrict__ my_idx, int world,
                                                              int rank, int T, int r_out, int k, int experts_per_rank,
                                                              float* __restrict__ rank_accum) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int pieces = (r_out + 127) / 128;
+  const int job = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int t = job / pieces, c0 = (job - t * pieces) * 128 + lane * 4;
   if (t >= T) return;
   const size_t u = static_cast<size_t>(rank) * T + t;
   unsigned need = 0;
@@ -81,16 +77,20 @@ __global__ void __launch_bounds__(256) ep_pull_reduce_kernel(EpPeers PART, const
     if (d >= 0 && d < world) need = 1u << d;
   }
   need = __reduce_or_sync(0xffffffffu, need);
-  const int vec = r_out / 4;
-  for (int i = lane; i < vec; i += 32) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < world; ++s) {
-      if (!((need >> s) & 1u)) continue;
-      const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(PART.p[s]) + u * r_out)[i];
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    reinterpret_cast<float4*>(rank_accum + static_cast<size_t>(t) * r_out)[i] = acc;
+  if (c0 >= r_out) return;
+  float4 v[EP_MAX_WORLD];
+#pragma unroll
+  for (int s = 0; s < EP_MAX_WORLD; ++s) {
+    v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (s < world && ((need >> s) & 1u)) v[s] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(PART.p[s]) + u * r_out + c0);
   }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int s = 0; s < EP_MAX_WORLD; ++s) {
+    // (a rank that did not contribute adds an exact zero: the sum is the same as if it were skipped)
+    acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w;
+  }
+  *reinterpret_cast<float4*>(rank_accum + static_cast<size_t>(t) * r_out + c0) = acc;
 }
 
 // Barrier across the ranks of one box, stream-ordered: one block, thread g talks to rank g.  Every rank keeps, per
@@ -168,7 +168,9 @@ extern "C" int bm_ep_push(void* const* h_bufs, void* const* route_bufs, int32_t 
     H.p[g] = h_bufs[g];
     R.p[g] = route_bufs[g];
   }
-  ep_push_kernel<<<(T + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(H, R, world, rank, T, r, k, experts_per_rank);
+  const int64_t pairs = static_cast<int64_t>(T) * world;
+  ep_push_kernel<<<static_cast<unsigned>((pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(H, R, world, rank, T, r, k,
+                                                                                                       experts_per_rank);
   BM_LAUNCH_CHECK("ep_push_kernel");
   return BM_OK;
 }
@@ -187,8 +189,9 @@ extern "C" int bm_ep_pull_reduce(void* const* part_bufs, const int32_t* my_topk_
                "ep_pull_reduce: buffer of rank %d is null or misaligned", g);
     P.p[g] = part_bufs[g];
   }
-  ep_pull_reduce_kernel<<<(T + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(P, my_topk_idx, world, rank, T, r_out, k,
-                                                                                   experts_per_rank, rank_accum);
+  const int64_t jobs = static_cast<int64_t>(T) * ((r_out + 127) / 128);
+  ep_pull_reduce_kernel<<<static_cast<unsigned>((jobs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      P, my_topk_idx, world, rank, T, r_out, k, experts_per_rank, rank_accum);
   BM_LAUNCH_CHECK("ep_pull_reduce_kernel");
   return BM_OK;
 }

@@ -19,15 +19,6 @@ constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KB
 // narrow output, e.g. the basis projection of 2048 tokens: 32 CTAs against 128).
 __host__ __device__ constexpr int tc_stage_bytes(int bn) { return TC_A_BYTES + bn * TC_BK * 2; }
 
-struct GemmTcArgs {
-  const void* X;          // [M, K]
-  const __half* W[2];     // [N, K] each
-  void* C[2];             // [M, N] each
-  const void* residual;   // [M, N] (W[0] only) or null
-  int M, N, K;
-  int x_dtype, c_dtype;
-  int* status;
-};
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const uint32_t dst = tc::smem_u32(smem);

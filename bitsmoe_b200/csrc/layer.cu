@@ -40,16 +40,6 @@ struct SkinnyArgs {
 };
 int launch_skinny_nt(SkinnyArgs a, cudaStream_t st);
 constexpr int SKINNY_MAX_TOKENS = 256;
-struct GemmTcArgs {
-  const void* X;
-  const __half* W[2];
-  void* C[2];
-  const void* residual;
-  int M, N, K;
-  int x_dtype, c_dtype;
-  int* status;
-};
-int launch_gemm_tc(const GemmTcArgs& a, int problems, cudaStream_t st);
 void plan_fast(const bm_layer* L, size_t base_bytes, FastPlan* P);
 int build_fast(bm_layer* L, const FastPlan& P, cudaStream_t st);
 size_t fast_build_scratch_bytes(const FastPlan& P);
@@ -444,7 +434,7 @@ static int basis_project_impl(const bm_layer_t* L, const void* x, int x_dtype, i
     GemmTcArgs t{};
     t.X = x; t.W[0] = L->vh_gate; t.W[1] = L->vh_up; t.C[0] = h_gate; t.C[1] = h_up; t.residual = nullptr;
     t.M = T; t.N = L->rank_in; t.K = L->hidden; t.x_dtype = x_dtype; t.c_dtype = BM_F16; t.status = L->status_dev;
-    return launch_gemm_tc(t, 2, static_cast<cudaStream_t>(stream));
+    return launch_gemm_basis(t, 2, static_cast<cudaStream_t>(stream));
   }
   GemmArgs g{};
   g.A[0] = g.A[1] = x;
@@ -562,7 +552,7 @@ extern "C" int bm_combine_down_basis(const bm_layer_t* L, const float* rank_accu
     GemmTcArgs t{};
     t.X = rank_accum; t.W[0] = t.W[1] = L->u_down; t.C[0] = t.C[1] = y; t.residual = residual;
     t.M = T; t.N = L->hidden; t.K = L->rank_out; t.x_dtype = BM_F32; t.c_dtype = y_dtype; t.status = L->status_dev;
-    return launch_gemm_tc(t, 1, static_cast<cudaStream_t>(stream));
+    return launch_gemm_basis(t, 1, static_cast<cudaStream_t>(stream));
   }
   GemmArgs g{};
   g.A[0] = g.A[1] = rank_accum;
