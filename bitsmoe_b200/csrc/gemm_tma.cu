@@ -10,7 +10,7 @@
 //               accumulator alternates between two TMEM buffers, so the next tile's products run while this tile's
 //               accumulator is read out
 //   warps 4-11  epilogue: tcgen05.ld, residual, rounding, stores of whole 64- or 128-byte row pieces
-//   warps 12-15 only for bf16 / fp32 activations: round the landed X slice to fp16 in place (both MMA operands have to
+//   warps 12-15, 2, 3  only for bf16 / fp32 activations: round the landed X slice to fp16 in place (both MMA operands have to
 //               be fp16: a bf16 A with an fp16 B is not an encodable instruction).  bf16 -> fp16 is element for
 //               element; an fp32 slice is twice as large as its fp16 result, and the eight lanes that hold a row read
 //               the row's 256 bytes before any of them writes its 16-byte piece of the 128-byte result row.
@@ -23,8 +23,8 @@
 namespace bm {
 
 
-constexpr int GT_BM = 128, GT_BK = 64, GT_THREADS = 512, GT_MAX_STAGES = 4;
-constexpr int GT_WARP_EPI0 = 4, GT_EPI_WARPS = 8, GT_WARP_TR0 = 12, GT_TR_WARPS = 4;
+constexpr int GT_BM = 128, GT_BK = 64, GT_THREADS = 512, GT_MAX_STAGES = 8;
+constexpr int GT_WARP_EPI0 = 4, GT_EPI_WARPS = 8, GT_WARP_TR0 = 12, GT_TR_WARPS = 6;    // transform: warps 12-15 and 2, 3
 
 __host__ __device__ constexpr int gt_a_bytes(int xd) { return xd == BM_F32 ? GT_BM * GT_BK * 4 : GT_BM * GT_BK * 2; }
 __host__ __device__ constexpr int gt_stage_bytes(int bn, int xd) { return gt_a_bytes(xd) + bn * GT_BK * 2; }
@@ -135,10 +135,10 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tma_kernel(const __grid_co
       if (ok && lane == 0) tc::mma_commit(&acc_full[ab]);
       __syncwarp();
     }
-  } else if (warp >= GT_WARP_TR0) {
+  } else if (warp >= GT_WARP_TR0 || warp == 2 || warp == 3) {
     // ------------------------------------------------------------------ rounding of the X slice to fp16, in place
     if (XD != BM_F16) {
-      const int tw = warp - GT_WARP_TR0;
+      const int tw = warp >= GT_WARP_TR0 ? warp - GT_WARP_TR0 : warp + 2;      // 0 .. 5
       uint32_t st = 0, ph = 0;
       for (int tile = blockIdx.x; tile < p.ntiles && ok; tile += gridDim.x) {
         for (int s = 0; s < nslices; ++s) {
@@ -146,9 +146,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tma_kernel(const __grid_co
           unsigned char* sa = smem + st * STAGE;
           if (XD == BM_BF16) {
             // 1024 pieces of 16 bytes, element for element (the swizzle only permutes whole pieces)
-#pragma unroll
-            for (int i = 0; i < (GT_BM * GT_BK * 2 / 16) / (GT_TR_WARPS * 32); ++i) {
-              uint4* q = reinterpret_cast<uint4*>(sa) + (i * GT_TR_WARPS + tw) * 32 + lane;
+#pragma unroll 2
+            for (int i = tw * 32 + lane; i < GT_BM * GT_BK * 2 / 16; i += GT_TR_WARPS * 32) {
+              uint4* q = reinterpret_cast<uint4*>(sa) + i;
               const uint4 v = *q;
               const uint32_t w[4] = {v.x, v.y, v.z, v.w};
               __half2 h[4];
@@ -160,8 +160,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tma_kernel(const __grid_co
             // row r, values 8 j .. 8 j + 7: two 16-byte pieces of box j / 4 -> piece j of the result row
             const int j = lane & 7;
 #pragma unroll 2
-            for (int it = 0; it < GT_BM / (GT_TR_WARPS * 4); ++it) {
-              const int r = (it * GT_TR_WARPS + tw) * 4 + (lane >> 3), sw = r & 7;
+            for (int rg = tw; rg < GT_BM / 4; rg += GT_TR_WARPS) {
+              const int r = rg * 4 + (lane >> 3), sw = r & 7;
               const unsigned char* box = sa + (j >> 2) * (A_BYTES / 2) + r * 128;
               const int c4 = 2 * (j & 3);
               const float4 lo = *reinterpret_cast<const float4*>(box + ((c4 ^ sw) << 4));
