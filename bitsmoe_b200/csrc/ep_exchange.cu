@@ -26,35 +26,56 @@ struct EpPeers {
   void* p[EP_MAX_WORLD];
 };
 
-// One warp per (local token, destination rank): the stores to one peer are independent of those to the others, and
-// a warp per pair keeps seven times as many of them in flight as a warp that walks the destinations.
+// One warp per local token.  The token's two rows are staged in shared memory once and then sent by the bulk-copy
+// engine, one copy per row and destination rank (512 bytes at r = 256): the engine moves whole rows as large
+// transactions, where the lanes' 16-byte stores cross the links as many small ones.  Rows whose size is not a multiple
+// of 16 bytes would need the plain path; the launcher requires r % 8 == 0.
 __global__ void __launch_bounds__(256) ep_push_kernel(EpPeers H, EpPeers R, int world, int rank, int T, int r, int k,
                                                       int experts_per_rank) {
+  extern __shared__ __align__(128) unsigned char push_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pair = blockIdx.x * (blockDim.x >> 5) + warp;
-  const int t = pair / world, d = pair - t * world;
-  if (t >= T || d == rank) return;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
   const size_t GT = static_cast<size_t>(world) * T;
   const size_t u = static_cast<size_t>(rank) * T + t;
   const int32_t* my_idx = reinterpret_cast<const int32_t*>(R.p[rank]) + u * k;
   const int32_t* my_w = reinterpret_cast<const int32_t*>(R.p[rank]) + (GT + u) * k;
-  // does rank d own one of the token's experts?
+  const uint32_t row_bytes = static_cast<uint32_t>(r) * 2u;
+  unsigned char* stage = push_smem + static_cast<size_t>(warp) * 2 * row_bytes;
+  // destinations of this token: owners of its experts
   unsigned need = 0;
+  int32_t id = -1, wbits = 0;
   if (lane < k) {
-    const int32_t id = my_idx[lane];
-    // routing of every token goes to every rank (its routing build walks all tokens of the wave)
-    reinterpret_cast<int32_t*>(R.p[d])[u * k + lane] = id;
-    reinterpret_cast<int32_t*>(R.p[d])[(GT + u) * k + lane] = my_w[lane];
-    need = id >= 0 && id / experts_per_rank == d ? 1u : 0u;
+    id = my_idx[lane];
+    wbits = my_w[lane];
+    const int d = id >= 0 ? id / experts_per_rank : -1;
+    if (d >= 0 && d < world) need = 1u << d;
   }
-  if (!__any_sync(0xffffffffu, need)) return;
+  need = __reduce_or_sync(0xffffffffu, need) & ~(1u << rank);
   const uint4* src_g = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(H.p[rank]) + u * r);
   const uint4* src_u = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(H.p[rank]) + (GT + u) * r);
-  uint4* dst_g = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(H.p[d]) + u * r);
-  uint4* dst_u = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(H.p[d]) + (GT + u) * r);
-  for (int i = lane; i < r / 8; i += 32) {
-    dst_g[i] = src_g[i];
-    dst_u[i] = src_u[i];
+  if (need) {
+    for (int i = lane; i < r / 8; i += 32) {
+      reinterpret_cast<uint4*>(stage)[i] = src_g[i];
+      reinterpret_cast<uint4*>(stage + row_bytes)[i] = src_u[i];
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+  // routing of every token goes to every rank (its routing build walks all tokens of the wave)
+  for (int d = 0; d < world; ++d) {
+    if (d == rank || lane >= k) continue;
+    reinterpret_cast<int32_t*>(R.p[d])[u * k + lane] = id;
+    reinterpret_cast<int32_t*>(R.p[d])[(GT + u) * k + lane] = wbits;
+  }
+  if (lane < world && ((need >> lane) & 1u)) {
+    __half* dst_g = reinterpret_cast<__half*>(H.p[lane]) + u * r;
+    __half* dst_u = reinterpret_cast<__half*>(H.p[lane]) + (GT + u) * r;
+    const uint32_t s0 = static_cast<uint32_t>(__cvta_generic_to_shared(stage));
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_g), "r"(s0), "r"(row_bytes) : "memory");
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_u), "r"(s0 + row_bytes), "r"(row_bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // the copies are complete before the thread exits
   }
 }
 
@@ -168,9 +189,9 @@ extern "C" int bm_ep_push(void* const* h_bufs, void* const* route_bufs, int32_t 
     H.p[g] = h_bufs[g];
     R.p[g] = route_bufs[g];
   }
-  const int64_t pairs = static_cast<int64_t>(T) * world;
-  ep_push_kernel<<<static_cast<unsigned>((pairs + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(H, R, world, rank, T, r, k,
-                                                                                                       experts_per_rank);
+  const size_t push_smem = static_cast<size_t>(8) * 2 * r * 2;     // two rows per warp
+  BM_REQUIRE(push_smem <= 48 * 1024, BM_ERR_UNSUPPORTED, "ep_push: rank %d too large for the staging buffer", r);
+  ep_push_kernel<<<(T + 7) / 8, 256, push_smem, static_cast<cudaStream_t>(stream)>>>(H, R, world, rank, T, r, k, experts_per_rank);
   BM_LAUNCH_CHECK("ep_push_kernel");
   return BM_OK;
 }
