@@ -599,7 +599,7 @@ def decode_arm(args):
 def ep_arm(args):
     """Strong scaling of one Qwen3-Next-80B-A3B-shaped layer over the ranks: see the module docstring."""
     from bitsmoe_b200 import capi, ep, synth
-    from bitsmoe_b200.layer import PackedLayer
+    from bitsmoe_b200.layer import PackedLayer, dense_mlp
     rank, world, local = dist_env()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -623,7 +623,7 @@ def ep_arm(args):
 
     # every rank generates the same weight sets (same seeds) and keeps only its experts
     synth_layers = [synth.make_layer(cfg, seed=42 + i, device=dev) for i in range(L)]
-    shared = [{k: v.to(dev, torch.bfloat16) for k, v in s.shared.items()} for s in synth_layers]
+    shared = [{k: v.to(dev, torch.float16) for k, v in s.shared.items()} for s in synth_layers]
 
     def local_layer(s):
         t = ep.shard_tables(s.tables, rank, world)
@@ -634,9 +634,9 @@ def ep_arm(args):
         if world > 1 else None
 
     def shared_expert(x, sh):
-        """sigmoid(x . w_g) * MLP(x) of the gated shared expert: dense bf16 (library GEMMs), added as the residual."""
-        y = (torch.nn.functional.silu(x @ sh["gate"].T) * (x @ sh["up"].T)) @ sh["down"].T
-        return torch.sigmoid(x @ sh["gate_logit_w"].T) * y
+        """sigmoid(x . w_g) * MLP(x) of the gated shared expert on this library's dense kernels (bm_dense_mlp_forward:
+        fp16 weights, tcgen05 GEMMs), added as the residual."""
+        return dense_mlp(x, sh["gate"], sh["up"], sh["down"], sh["gate_logit_w"])
 
     xs = [synth.activations(cfg, T_loc, seed=7 + i + 1000 * rank, device=dev) for i in range(L)]
     lg = [synth.router_logits(cfg, T_loc, seed=9 + i + 1000 * rank, device=dev) for i in range(L)]
