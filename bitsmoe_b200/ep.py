@@ -370,7 +370,8 @@ class SymmetricExpertParallel:
         """One wave on the current stream: x [T, H], logits [T, E] of this rank's tokens -> out [T, H].
 
         ``residual_fn(x) -> [T, H]`` (e.g. a dense shared expert) runs on a side stream beside the exchange and the
-        barriers, where the GPU is mostly idle; the wave waits for it only before the final down-basis product."""
+        barriers, where the GPU is mostly idle (it starts once the basis projection is queued); the wave waits for it
+        only before the final down-basis product."""
         capi, lib, pk = self._capi, self._capi.lib(), self.packed
         G, T, k, r, r_out = self.world, self.T, self.top_k, pk.rank_in, pk.rank_out
         if x.shape[0] != T:
@@ -381,18 +382,20 @@ class SymmetricExpertParallel:
         st = capi.stream_ptr(pk.device)
         x, logits = x.contiguous(), logits.contiguous()
         with torch.cuda.device(pk.device):
-            if residual_fn is not None:
-                main, side = torch.cuda.current_stream(pk.device), self._side[area]
-                side.wait_stream(main)
-                with torch.cuda.stream(side):
-                    residual = residual_fn(x)
-                    residual.record_stream(main)
             idx_mine, w_mine = rt[0, self.rank], rt[1, self.rank]
             capi.check(lib.bm_route_topk(logits.data_ptr(), capi.dtype_code(logits.dtype), T, logits.shape[1], k,
                                          int(bool(self.norm_topk_prob)), capi.round_code(weight_dtype), idx_mine.data_ptr(),
                                          w_mine.data_ptr(), st))
             capi.check(lib.bm_basis_project(pk._handle, x.data_ptr(), capi.dtype_code(x.dtype), T, h[0, self.rank].data_ptr(),
                                             h[1, self.rank].data_ptr(), st))
+            if residual_fn is not None:
+                # forked here, after the projection: the side stream's GEMMs then run beside the push, the barrier and
+                # the routing build, which leave most SMs idle, instead of competing with the projection
+                main, side = torch.cuda.current_stream(pk.device), self._side[area]
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    residual = residual_fn(x)
+                    residual.record_stream(main)
             capi.check(lib.bm_ep_push(h_tab, r_tab, G, self.rank, T, r, k, self.per, st))
             capi.check(lib.bm_ep_barrier(pk._handle, self._flags, G, self.rank, 2 * area, self.barrier_limit_ms, st))
             capi.check(lib.bm_route_build(rt[0].data_ptr(), rt[1].data_ptr(), self.g2l.data_ptr(), self.g2l.numel(), G * T, k,
