@@ -1,4 +1,5 @@
-// Shared-basis products for large token counts on the 5th-generation tensor cores:
+// Shared-basis products for large token counts on the 5th-generation tensor cores: the cp.async variant, taken when
+// a shape or a pointer does not suit the tiled copies of gemm_tma.cu (which is tried first, see launch_gemm_basis).
 //   C[m][n] = sum_k X[m][k] * W[n][k],  X = activations (rows = tokens), W = fp16 basis matrix.
 //   h_gate / h_up = x . Vh^T  (bitsmoe/models/qwen3moe/bitsmoe_block.py:63-64)
 //   y = fp16(rank_accum) . U_down^T (+ residual)  (bitsmoe/models/base_block.py:414)

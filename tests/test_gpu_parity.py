@@ -463,7 +463,10 @@ def test_bounded_wait_gives_up_and_reports_timeout(q30_small):
 
 
 @pytest.mark.parametrize("T,E,H,dtype", [(1, 128, 2048, torch.bfloat16), (64, 128, 2048, torch.bfloat16), (64, 512, 2048, torch.float16),
-                                         (7, 64, 2048, torch.float16), (1000, 128, 2048, torch.bfloat16), (33, 24, 384, torch.float32)])
+                                         (7, 64, 2048, torch.float16), (1000, 128, 2048, torch.bfloat16), (33, 24, 384, torch.float32),
+                                         # the tiled-copy GEMM: ragged rows, ragged and narrow outputs, one K slice, every input type
+                                         (300, 72, 192, torch.float32), (1000, 520, 2048, torch.float16), (5000, 128, 64, torch.bfloat16),
+                                         (257, 8, 128, torch.float16), (2100, 264, 320, torch.float32), (20000, 512, 128, torch.bfloat16)])
 def test_gate_logits_vs_fp64(T, E, H, dtype):
     """Router logits x @ W_gate^T on the library's kernels (cluster split-K for decode sizes, tcgen05 above)."""
     from bitsmoe_b200.layer import gate_logits
