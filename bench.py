@@ -61,7 +61,9 @@ def parse():
     ap.add_argument("--prefill-tokens", type=int, default=8192)
     ap.add_argument("--ep-tokens", type=int, default=16384, help="tokens of one step of the ep workload, over all GPUs")
     ap.add_argument("--ep-layers", type=int, default=4, help="distinct weight sets rotated through (ep workload)")
-    ap.add_argument("--waves", type=int, default=2, help="ep workload: waves per step and rank (exchange of one beside compute of the other)")
+    ap.add_argument("--waves", type=int, default=1,
+                    help="ep workload: waves per step and rank (2: the exchange of one runs beside the compute of the other; "
+                         "measured no faster than 1 at the default sizes)")
     ap.add_argument("--no-extras", action="store_true", help="headline only (skip other batch sizes / prefill / cpu / reference kernels)")
     ap.add_argument("--path", type=int, default=0, help="experts path: 0 auto, 1 generic, 2 decode, 3 tensor")
     ap.add_argument("--probe", default=None, choices=["experts", "forward"],
