@@ -1,8 +1,9 @@
 // Packed routed-expert forward for large token counts (prefill): fused mixed-bit grouped GEMM on the
 // 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
-// Work item = (expert, block of up to NT of its assignments; NT <= 128 is chosen per layer so that the activation
-// operand of an item and enough copy / conversion stages fit in shared memory).  One persistent CTA per SM walks the
+// Work item = (expert, block of up to NT of its assignments; NT -- 64 where it fits -- is chosen per layer so that the
+// activation operand of an item, two z tiles and enough copy / conversion stages fit in shared memory and seven
+// accumulators of NT columns fit in tensor memory).  One persistent CTA per SM walks the
 // items.  For an item the three products of every 128-column tile run with the WEIGHTS as the 128-row operand:
 //   gate/up:  D_g[c, n] = sum_slot  W_g[c, slot] * act_g[n, slot]      (M = 128 columns c, N = the item's tokens)
 //   down:     D_d[slot, n] += sum_c W_d[slot, c] * z[n, c]             (M = 128 row slots x 2 or 3, same N)
@@ -10,8 +11,9 @@
 // once per item, so the conversion work per token falls with NT.  D_d accumulates over all tiles in TMEM.
 // Warp roles (608 threads):
 //   warps 0-7   epilogue (two per TMEM lane quarter, alternate 32-token column chunks): tcgen05.ld D_g/D_u ->
-//               z = silu(g)*u -> fp16 z tile in shared memory; at the end of the item D_d -> * s * route weight ->
-//               fp32 atomics into rank_accum.  Warp 0 also looks up the next item while the current one runs.
+//               z = silu(g)*u -> fp16 z tile in shared memory; at the end of the item D_d * s * route weight is
+//               transposed through the idle operand ring and added to rank_accum row by row (16-byte vector
+//               reductions).  Warp 0 also looks up the next item while the current one runs.
 //   warp  8     producer: cp.async.bulk of the packed words + scales of (tile, matrix) sections into a ring of slots
 //   warps 9,10  MMA issue, one thread each.  tcgen05.mma blocks its thread until the tensor pipe accepts it, so the
 //               waits and commits around a stage cost tensor time when one thread issues everything; two pipelines
