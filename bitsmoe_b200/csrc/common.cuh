@@ -1,6 +1,7 @@
 // Shared declarations of the bitsmoe_b200 library (host + device).
 #pragma once
 
+#include <nvtx3/nvToolsExt.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -176,6 +177,15 @@ inline int launch_gemm_basis(const GemmTcArgs& a, int problems, cudaStream_t st)
   const int rc = launch_gemm_tma(a, problems, st);
   return rc == BM_ERR_UNSUPPORTED ? launch_gemm_tc(a, problems, st) : rc;
 }
+
+// NVTX range around a public entry point (route / projection / experts / combine / exchange show up as named ranges
+// in a timeline tool; without a tool attached a push or pop is one null-pointer test).
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 }  // namespace bm
 

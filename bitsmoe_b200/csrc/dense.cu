@@ -99,6 +99,7 @@ using namespace bm;
 
 extern "C" int bm_gate_logits(const void* x, int x_dtype, const uint16_t* gate_w, int32_t T, int32_t num_routed, int32_t hidden,
                               void* logits, int logits_dtype, void* stream) {
+  bm::NvtxRange nvtx_range("bm_gate_logits");
   BM_REQUIRE(T >= 0 && num_routed > 0 && hidden > 0, BM_ERR_INVALID_ARG, "gate_logits: bad sizes");
   BM_REQUIRE(x_dtype >= BM_F16 && x_dtype <= BM_F32 && logits_dtype >= BM_F16 && logits_dtype <= BM_F32, BM_ERR_INVALID_ARG,
              "gate_logits: bad dtype");
@@ -117,6 +118,7 @@ extern "C" size_t bm_dense_mlp_workspace_bytes(int32_t T, int32_t intermediate) 
 extern "C" int bm_dense_mlp_forward(const void* x, int x_dtype, const uint16_t* w_gate, const uint16_t* w_up, const uint16_t* w_down,
                                     const uint16_t* token_gate_w, int32_t T, int32_t hidden, int32_t intermediate,
                                     const void* residual, void* y, int y_dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  bm::NvtxRange nvtx_range("bm_dense_mlp_forward");
   BM_REQUIRE(T >= 0 && hidden > 0 && intermediate > 0 && intermediate % 2 == 0, BM_ERR_INVALID_ARG, "dense_mlp: bad sizes");
   BM_REQUIRE(x_dtype >= BM_F16 && x_dtype <= BM_F32 && y_dtype >= BM_F16 && y_dtype <= BM_F32, BM_ERR_INVALID_ARG, "dense_mlp: bad dtype");
   if (T == 0) return BM_OK;

@@ -158,6 +158,7 @@ extern "C" size_t bm_ep_flag_bytes(void) { return sizeof(uint32_t) * bm::EP_CHAN
 
 extern "C" int bm_ep_barrier(const bm_layer_t* layer, void* const* flag_bufs, int32_t world, int32_t rank, int32_t channel,
                              int32_t limit_ms, void* stream) {
+  bm::NvtxRange nvtx_range("bm_ep_barrier");
   using namespace bm;
   BM_REQUIRE(layer && layer->status_dev && flag_bufs, BM_ERR_INVALID_ARG, "ep_barrier: null pointer");
   BM_REQUIRE(world >= 1 && world <= EP_MAX_WORLD && rank >= 0 && rank < world && channel >= 0 && channel < EP_CHANNELS,
@@ -177,6 +178,7 @@ extern "C" int bm_ep_barrier(const bm_layer_t* layer, void* const* flag_bufs, in
 
 extern "C" int bm_ep_push(void* const* h_bufs, void* const* route_bufs, int32_t world, int32_t rank, int32_t T, int32_t r,
                           int32_t k, int32_t experts_per_rank, void* stream) {
+  bm::NvtxRange nvtx_range("bm_ep_push");
   using namespace bm;
   BM_REQUIRE(h_bufs && route_bufs, BM_ERR_INVALID_ARG, "ep_push: null pointer table");
   BM_REQUIRE(world >= 1 && world <= EP_MAX_WORLD && rank >= 0 && rank < world, BM_ERR_INVALID_ARG, "ep_push: bad world / rank");
@@ -198,6 +200,7 @@ extern "C" int bm_ep_push(void* const* h_bufs, void* const* route_bufs, int32_t 
 
 extern "C" int bm_ep_pull_reduce(void* const* part_bufs, const int32_t* my_topk_idx, int32_t world, int32_t rank, int32_t T,
                                  int32_t r_out, int32_t k, int32_t experts_per_rank, float* rank_accum, void* stream) {
+  bm::NvtxRange nvtx_range("bm_ep_pull_reduce");
   using namespace bm;
   BM_REQUIRE(part_bufs && my_topk_idx && rank_accum, BM_ERR_INVALID_ARG, "ep_pull_reduce: null pointer");
   BM_REQUIRE(world >= 1 && world <= EP_MAX_WORLD && rank >= 0 && rank < world, BM_ERR_INVALID_ARG, "ep_pull_reduce: bad world / rank");

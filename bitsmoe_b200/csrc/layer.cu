@@ -454,6 +454,7 @@ static int basis_project_impl(const bm_layer_t* L, const void* x, int x_dtype, i
 
 extern "C" int bm_basis_project(const bm_layer_t* L, const void* x, int x_dtype, int32_t T, uint16_t* h_gate,
                                 uint16_t* h_up, void* stream) {
+  bm::NvtxRange nvtx_range("bm_basis_project");
   return basis_project_impl(L, x, x_dtype, T, h_gate, h_up, nullptr, 0, nullptr, stream);
 }
 
@@ -525,12 +526,14 @@ extern "C" int bm_experts_forward(const bm_layer_t* L, const uint16_t* h_gate, c
                                   const int32_t* token_indices, const int32_t* expert_offsets,
                                   const float* route_weights, int32_t T, int32_t num_assign, float* rank_accum,
                                   int32_t path, void* workspace, size_t workspace_bytes, void* stream) {
+  bm::NvtxRange nvtx_range("bm_experts_forward");
   return experts_forward_impl(L, h_gate, h_up, token_indices, expert_offsets, route_weights, T, num_assign, rank_accum, path,
                               false, workspace, workspace_bytes, stream);
 }
 
 extern "C" int bm_combine_down_basis(const bm_layer_t* L, const float* rank_accum, int32_t T, const void* residual,
                                      void* y, int y_dtype, void* stream) {
+  bm::NvtxRange nvtx_range("bm_combine_down_basis");
   BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "combine: null layer");
   BM_REQUIRE(L->u_down, BM_ERR_INVALID_ARG, "missing shared_u_down for packed routed experts");
   BM_REQUIRE(T >= 0 && y_dtype >= BM_F16 && y_dtype <= BM_F32, BM_ERR_INVALID_ARG, "combine: bad arguments");
@@ -577,6 +580,7 @@ extern "C" int bm_layer_forward(const bm_layer_t* L, const void* x, int x_dtype,
                                 int32_t T, int32_t num_routed, int32_t k, int32_t renorm, int32_t weight_round,
                                 const int32_t* global_to_local, const void* residual, void* y, int32_t path,
                                 void* workspace, size_t workspace_bytes, void* stream) {
+  bm::NvtxRange nvtx_range("bm_layer_forward");
   BM_REQUIRE(L != nullptr, BM_ERR_INVALID_ARG, "layer_forward: null layer");
   BM_REQUIRE(T >= 0 && k > 0 && num_routed > 0, BM_ERR_INVALID_ARG, "layer_forward: bad sizes");
   BM_REQUIRE(global_to_local != nullptr || num_routed == L->num_experts, BM_ERR_INVALID_ARG,

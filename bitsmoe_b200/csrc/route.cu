@@ -352,6 +352,7 @@ __global__ void __launch_bounds__(ROUTE_BLOCK) route_scatter_kernel(
 
 extern "C" int bm_route_topk(const void* logits, int logits_dtype, int32_t T, int32_t E, int32_t k, int32_t renorm,
                              int32_t weight_round, int32_t* topk_idx, float* topk_w, void* stream) {
+  bm::NvtxRange nvtx_range("bm_route_topk");
   using namespace bm;
   BM_REQUIRE(T >= 0 && E > 0 && k > 0, BM_ERR_INVALID_ARG, "route_topk: bad sizes T=%d E=%d k=%d", T, E, k);
   BM_REQUIRE(k <= 32 && k <= E, BM_ERR_UNSUPPORTED, "route_topk: top_k=%d must be <= min(32, E=%d)", k, E);
@@ -387,6 +388,7 @@ extern "C" int bm_route_build(const int32_t* topk_idx, const float* topk_w, cons
                               int32_t k, int32_t num_local, int32_t tile_rows, int32_t* token_indices,
                               int32_t* expert_offsets, float* route_flat, int32_t* tile_table, int32_t* counts,
                               void* workspace, size_t workspace_bytes, void* stream) {
+  bm::NvtxRange nvtx_range("bm_route_build");
   using namespace bm;
   BM_REQUIRE(T >= 0 && k > 0 && num_local > 0 && num_routed > 0, BM_ERR_INVALID_ARG, "route_build: bad sizes");
   BM_REQUIRE(global_to_local != nullptr || num_routed == num_local, BM_ERR_INVALID_ARG,
@@ -439,6 +441,7 @@ extern "C" int bm_route(const void* logits, int logits_dtype, int32_t T, int32_t
                         int32_t* topk_idx, float* topk_w, int32_t* token_indices, int32_t* expert_offsets,
                         float* route_flat, int32_t* tile_table, int32_t* counts, void* workspace, size_t workspace_bytes,
                         void* stream) {
+  bm::NvtxRange nvtx_range("bm_route");
   using namespace bm;
   int rc = bm_route_topk(logits, logits_dtype, T, E_routed, k, renorm, weight_round, topk_idx, topk_w, stream);
   if (rc) return rc;
