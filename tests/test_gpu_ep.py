@@ -56,6 +56,17 @@ def _worker(rank, world, port, ret):
                 epl.packed.check_status()
                 helpers.assert_close(y_ep, y_one, what=f"rank {rank}: peer-memory exchange, waves of {wave}, overlap={overlap}")
                 helpers.assert_detects_damage(y_ep - res.float(), y_one.float() - res.float())
+            # a dense part handed in as residual_fn runs on the side stream beside the exchange and joins before the
+            # down basis: same result as the same function computed up front (several GEMMs, so that a missing join shows)
+            gw = torch.Generator(device="cpu").manual_seed(77)
+            wa = (torch.randn(cfg.hidden, cfg.hidden, generator=gw) * 0.02).to(dev, torch.bfloat16)
+            dense = lambda xw: (((xw @ wa) @ wa) @ wa) * 0.05
+            y_one_fn = full.forward(x, logits, cfg.top_k, True, torch.bfloat16, residual=dense(x))
+            for overlap in (False, True):
+                y_ep = sym.forward(x, logits, torch.bfloat16, overlap=overlap, residual_fn=dense)
+                torch.cuda.synchronize()
+                epl.packed.check_status()
+                helpers.assert_close(y_ep, y_one_fn, what=f"rank {rank}: residual_fn on the side stream, waves of {wave}, overlap={overlap}")
             # the combine at rank_accum level: pulled sum == single-GPU rank_accum of the same tokens (last wave)
             idx, w = full.route_topk(logits[-wave:], cfg.top_k, True, torch.bfloat16)
             from bitsmoe_b200.layer import route_build
